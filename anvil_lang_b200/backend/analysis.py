@@ -1,0 +1,148 @@
+"""Static questions about a kernel that decide how it may be scheduled on the device.
+
+`parallel_safe` restates the reference's rule for when every output element may run in its own
+thread (anvil/backend/cuda.py:380-395, with `injective_over` :618-633 and `kernel_loads` :597-615).
+The rest (contiguity, vector width, arena plan) has no reference counterpart: the reference always
+runs one thread per output element with a scalar loop.
+"""
+from __future__ import annotations
+
+from .. import kir
+
+ALIGN = 256                  # arena alignment of every buffer, bytes
+
+
+def injective_over(off: kir.Affine, vars_) -> bool:
+    """Different values of `vars_` reach different offsets (mixed-radix argument: sorted by stride,
+    each stride must exceed the span of all smaller ones). Every var of extent > 1 must appear."""
+    items = []
+    for v in vars_:
+        if v.extent <= 1:
+            continue
+        c = off.coef(v)
+        if c == 0:
+            return False
+        items.append((abs(c), v.extent))
+    reach = 0
+    for c, n in sorted(items):
+        if c <= reach:
+            return False
+        reach += c * (n - 1)
+    return True
+
+
+def parallel_safe(k: kir.Kernel) -> bool:
+    """Can every output element run in its own thread, in any order?"""
+    written = {s.buf.root for s in k.stores}
+    for s in k.stores:
+        if s.accumulate:
+            continue                                 # an atomic (or exclusive) add
+        if s.offset.gathers():
+            return False                             # duplicate indices: the last write wins
+        if not injective_over(s.offset, k.domain):
+            return False                             # several elements write one place
+    for buf, off in k.loads():
+        if buf.root in written:
+            same = [s for s in k.stores if s.buf.root is buf.root]
+            if any(s.accumulate or s.offset != off for s in same):
+                return False                         # reads what other elements write
+    return True
+
+
+def exclusive_store(k: kir.Kernel, s: kir.Store) -> bool:
+    """An accumulating store that no two output elements share: a plain read-modify-write."""
+    return not s.offset.gathers() and injective_over(s.offset, k.domain)
+
+
+def stride_of(off: kir.Affine, v: kir.Var) -> int | None:
+    """Coefficient of `v` in `off`, or None when `v` also steers a gathered index."""
+    for g, _ in off.gathers():
+        if v in g.offset.vars():
+            return None
+    return off.coef(v)
+
+
+def aligned4(off: kir.Affine, v: kir.Var) -> bool:
+    """With `v` a multiple of 4, is the element offset a multiple of 4 (16-byte aligned access)?
+    Needs every other contribution to be a multiple of 4: constants, other strides, and the
+    coefficients of run-time terms."""
+    if off.const % 4:
+        return False
+    for t, c in off.terms:
+        if t is v:
+            continue
+        if c % 4:
+            return False
+    return True
+
+
+def offset_fits_i32(off: kir.Affine) -> bool:
+    b = off.bounds()
+    return b is not None and -(1 << 31) < b[0] and b[1] < (1 << 31) - 1
+
+
+def hot_loop(prog: kir.Program):
+    """The `For` whose body does the most kernel work: the training loop. Returns the For or None."""
+    best, best_w = None, 0
+
+    def weight(block: kir.Block) -> int:
+        w = 0
+        for s in block.stmts:
+            if isinstance(s, kir.KernelStmt):
+                w += 1
+            elif isinstance(s, kir.For):
+                w += weight(s.body) * trips(s)
+            elif isinstance(s, kir.While):
+                w += weight(s.body) + weight(s.cond_block)
+            elif isinstance(s, kir.If):
+                w += max(weight(s.then), weight(s.orelse))
+        return w
+
+    def trips(f: kir.For) -> int:
+        if isinstance(f.start, int) and isinstance(f.stop, int) and f.step > 0:
+            return max(0, (f.stop - f.start + f.step - 1) // f.step)
+        return 1
+
+    def visit(block: kir.Block, mult: int):
+        nonlocal best, best_w
+        for s in block.stmts:
+            if isinstance(s, kir.For):
+                inner_loops = any(isinstance(x, (kir.For, kir.While)) for b in kir.walk_blocks(s.body) for x in b.stmts)
+                w = weight(s.body) * trips(s) * mult
+                if not inner_loops and trips(s) > 1 and w > best_w:
+                    best, best_w = s, w
+                visit(s.body, mult * trips(s))
+            elif isinstance(s, kir.If):
+                visit(s.then, mult)
+                visit(s.orelse, mult)
+    visit(prog.main, 1)
+    return best
+
+
+class ArenaPlan:
+    """Byte offsets of every root buffer inside the runtime's arena. The header comes first, then a
+    scratch region for split reductions, then the buffers."""
+
+    def __init__(self, offsets: dict, size: int, scratch_off: int, scratch_bytes: int):
+        self.offsets = offsets
+        self.size = size
+        self.scratch_off = scratch_off
+        self.scratch_bytes = scratch_bytes
+
+    def off(self, b: kir.Buffer) -> int:
+        return self.offsets[b.root.id]
+
+
+def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256) -> ArenaPlan:
+    """Every root buffer gets its own zero-initialised, 256-byte aligned region (the reference gives
+    each buffer its own zeroed allocation, anvil/backend/cuda.py:416-421)."""
+    def up(n):
+        return (n + ALIGN - 1) // ALIGN * ALIGN
+    pos = up(header)
+    scratch_off = pos
+    pos += up(max(scratch_bytes, 4))
+    offsets = {}
+    for r in prog.roots():
+        offsets[r.id] = pos
+        pos += up(max(r.nbytes, 16))
+    return ArenaPlan(offsets, pos, scratch_off, up(max(scratch_bytes, 4)))

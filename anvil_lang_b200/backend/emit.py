@@ -1,0 +1,979 @@
+"""The sm_100a emitter: a `kir.Program` becomes one CUDA C++ translation unit.
+
+This is the counterpart of the reference's text emitter (anvil/backend/cuda.py: `KernelGen` :52-320
+for kernels, `CudaGen` :348-594 for host code), redesigned for B200:
+
+  * kernels are scheduled by class instead of always "one thread per output with a serial loop":
+      eltwise      128-bit vectorised single pass over the flattened domain
+      thread       short reductions (window max, 10-class argmax) stay in the thread
+      coop(row)    the reduction index is contiguous in memory: lanes of a warp (or a whole CTA)
+                   stride across it with 128-bit loads and combine with a fixed shuffle tree
+      coop(col)    the output index is contiguous: threads along outputs, a second block dimension
+                   along the reduction, shared-memory tree
+      split        few outputs x long reduction: several CTAs per output write partial results to
+                   arena scratch and a second kernel combines them in order
+      serial       order-dependent kernels run on one thread (anvil/backend/cuda.py:380-395)
+    All combination trees have a shape fixed by the launch geometry: results are bit-reproducible.
+  * every tensor lives at a fixed offset of one device arena; a kernel receives the arena base and
+    derives its pointers from compile-time offsets.
+  * host control flow is emitted as C++ that calls the runtime's C ABI (include/anvil_cuda.h); it
+    never touches device memory directly and synchronises only when the host needs a value
+    (a printed scalar, an `if`/`while` condition, a run-time loop bound).
+  * runs of kernel launches inside loops are recorded into CUDA graphs and replayed.
+
+Scalar expression semantics follow anvil/backend/cuda.py:110-199 (casts, wrap-around i32
+arithmetic, comparison results 0.0/1.0, nan-propagating max/min).
+"""
+from __future__ import annotations
+
+import math
+
+from .. import kir
+from ..kir import F32, I32
+from . import analysis as an
+
+THREADS = 256
+MAX_BLOCKS = 148 * 8
+
+
+def ctype(dt) -> str:
+    return "int" if dt == I32 else "float"
+
+
+def flit(v: float) -> str:
+    if math.isnan(v):
+        return "CUDART_NAN_F"
+    if math.isinf(v):
+        return "CUDART_INF_F" if v > 0 else "(-CUDART_INF_F)"
+    r = repr(float(v))
+    return f"{r}f" if ("e" in r or "." in r) else f"{r}.0f"
+
+
+def c_string(s: str) -> str:
+    out = []
+    for ch in s.encode("utf-8"):
+        c = chr(ch)
+        if c == "\\":
+            out.append("\\\\")
+        elif c == '"':
+            out.append('\\"')
+        elif c == "\n":
+            out.append("\\n")
+        elif c == "\t":
+            out.append("\\t")
+        elif 32 <= ch < 127 and c != "?":
+            out.append(c)
+        else:
+            out.append("\\%03o" % ch)
+    return '"' + "".join(out) + '"'
+
+
+RED_OP = {"sum": "anvil::OpSum", "prod": "anvil::OpProd", "max": "anvil::OpMax", "min": "anvil::OpMin"}
+
+
+class Scope:
+    """Builds the C++ for a kernel's expressions. `lanes` > 1 evaluates the body for that many
+    consecutive values of `vv`; nodes that do not depend on `vv` are computed once."""
+
+    def __init__(self, kg: "KernelGen", names: dict, lanes: int = 1, vv=None, ind: str = "        "):
+        self.kg = kg
+        self.names = names              # Var -> C identifier (lane l of vv is f"{name}_{l}")
+        self.lanes = lanes
+        self.vv = vv
+        self.ind = ind
+        self.lines: list[str] = []
+        self.memo: dict = {}
+        self.dep: dict = {}
+        self.lets: dict = {}            # let id -> {lane: code}
+        self.rand_idx = None            # C expression of the row-major domain index (per lane: callable)
+
+    # ---- which nodes vary along the vectorised var
+    def off_depends(self, a: kir.Affine) -> bool:
+        return self.vv is not None and self.vv in a.vars()
+
+    def depends(self, e: kir.E) -> bool:
+        if self.lanes == 1:
+            return False
+        hit = self.dep.get(id(e))
+        if hit is None:
+            if e.k in ("load", "index"):
+                hit = self.off_depends(e.off)
+            elif e.k == "rand":
+                hit = self.kg.rand_varies_with(self.vv)
+            elif e.k == "let":
+                hit = self.lets.get(e.let.id, {}).get("dep", False)
+            elif e.k == "acc":
+                hit = False
+            else:
+                hit = any(self.depends(x) for x in e.a)
+            self.dep[id(e)] = hit
+        return hit
+
+    def emit(self, s: str):
+        self.lines.append(self.ind + s)
+
+    def var(self, v: kir.Var, lane) -> str:
+        n = self.names[v]
+        if v is self.vv and self.lanes > 1:
+            return f"{n}_{lane}"
+        return n
+
+    # ---- affine offsets
+    def affine(self, a: kir.Affine, lane) -> str:
+        wide = not an.offset_fits_i32(a)
+        parts = [f"{a.const}{'L' if wide else ''}"] if a.const else []
+        for t, c in a.terms:
+            if isinstance(t, kir.Var):
+                x = self.var(t, lane)
+            elif isinstance(t, kir.SRef):
+                x = self.sref(t)
+            else:
+                x = self.gather(t, lane)
+            if wide:
+                parts.append(f"(long){x}" if c == 1 else f"{c}L * {x}")
+            else:
+                parts.append(x if c == 1 else f"{c} * {x}")
+        return " + ".join(parts) if parts else "0"
+
+    def sref(self, t: kir.SRef) -> str:
+        key = ("sref", t.buf.root.id)
+        hit = self.memo.get(key)
+        if hit is None:
+            hit = self.kg.tmp()
+            self.emit(f"const long {hit} = (long){self.kg.ptr(t.buf, False)}[0];")
+            self.memo[key] = hit
+        return hit
+
+    def gather(self, g: kir.Gather, lane) -> str:
+        dep = self.off_depends(g.offset)
+        key = ("g", g.key(), lane if dep else None)
+        hit = self.memo.get(key)
+        if hit is None:
+            hit = self.kg.tmp()
+            code = self.kg.gen.fault(f"index out of bounds ({g.where or 'gather'}; dimension size {g.bound})")
+            off = self.affine(g.offset, lane)
+            self.emit(f"const long {hit} = anvil::gather_index({self.kg.ptr(g.buf, False)}, {off}, "
+                      f"{g.lo}L, {g.hi}L, fault_, {code});")
+            self.memo[key] = hit
+        return hit
+
+    # ---- expressions
+    def ex(self, e: kir.E, lane=0) -> str:
+        if e.k == "const":
+            return flit(e.val) if e.dt == F32 else f"({int(e.val)})"
+        if e.k == "acc":
+            return "acc"
+        if e.k == "let":
+            d = self.lets[e.let.id]
+            return d[lane if d["dep"] else None]
+        dep = self.depends(e)
+        key = (e.key(), lane if dep else None)
+        hit = self.memo.get(key)
+        if hit is not None:
+            return hit
+        s = self.build(e, lane)
+        name = self.kg.tmp()
+        self.emit(f"const {ctype(e.dt)} {name} = {s};")
+        self.memo[key] = name
+        return name
+
+    def cast(self, e: kir.E, dt, lane) -> str:
+        s = self.ex(e, lane)
+        if e.dt == dt:
+            return s
+        return f"(float)({s})" if dt == F32 else f"anvil::f2i({s})"
+
+    def build(self, e: kir.E, lane) -> str:
+        k = e.k
+        if k == "load":
+            return self.load(e, lane)
+        if k == "index":
+            return f"(int)({self.affine(e.off, lane)})"
+        if k == "rand":
+            idx = self.kg.rand_index(self, lane)
+            return f"anvil_rand((uint32_t)({idx}), stream_, {e.salt}u, seed_, {1 if e.open_low else 0})"
+        if k == "un":
+            return self.unary(e, lane)
+        if k == "bin":
+            return self.binary(e, lane)
+        if k == "sel":
+            c = self.ex(e.a[0], lane)
+            return f"(({c}) != 0 ? {self.cast(e.a[1], e.dt, lane)} : {self.cast(e.a[2], e.dt, lane)})"
+        raise NotImplementedError(k)
+
+    def load(self, e: kir.E, lane) -> str:
+        p = self.kg.ptr(e.buf, False)
+        if self.lanes == 4 and self.depends(e) and an.stride_of(e.off, self.vv) == 1 and an.aligned4(e.off, self.vv):
+            vkey = ("vec", e.key())
+            q = self.memo.get(vkey)
+            if q is None:
+                q = self.kg.tmp("q")
+                self.emit(f"const {ctype(e.dt)}4 {q} = anvil::ld4({p} + ({self.affine(e.off, 0)}));")
+                self.memo[vkey] = q
+            return f"{q}.{'xyzw'[lane]}"
+        return f"{p}[{self.affine(e.off, lane)}]"
+
+    def unary(self, e: kir.E, lane) -> str:
+        op, x = e.op, e.a[0]
+        isint = x.dt == I32
+        a = self.ex(x, lane)
+        if op == "detach":
+            return a
+        if op == "neg":
+            return f"(-({a}))"
+        if op == "abs":
+            return f"abs({a})" if isint else f"fabsf({a})"
+        if op == "not":
+            return f"(({a}) == 0 ? 1.0f : 0.0f)"
+        if op == "f32":
+            return f"(float)({a})"
+        if op == "i32":
+            return a if isint else f"anvil::f2i({a})"
+        if op == "sign":
+            return f"anvil::isign({a})" if isint else f"anvil::fsign({a})"
+        if op in ("floor", "ceil", "round"):
+            return a if isint else {"floor": "floorf", "ceil": "ceilf", "round": "rintf"}[op] + f"({a})"
+        fa = f"(float)({a})" if isint else a
+        if op == "rsqrt":
+            return f"(1.0f / sqrtf({fa}))"
+        if op == "recip":
+            return f"(1.0f / ({fa}))"
+        if op == "sigmoid":
+            return f"anvil::sigmoid({fa})"
+        return {"exp": "expf", "log": "logf", "sqrt": "sqrtf", "tanh": "tanhf", "sin": "sinf", "cos": "cosf"}[op] + f"({fa})"
+
+    def binary(self, e: kir.E, lane) -> str:
+        op, x, y = e.op, e.a[0], e.a[1]
+        if op in kir.COMPARISONS or op in ("and", "or"):
+            a, b = self.ex(x, lane), self.ex(y, lane)
+            if op in ("and", "or"):
+                return f"((({a}) != 0 {'&&' if op == 'and' else '||'} ({b}) != 0) ? 1.0f : 0.0f)"
+            sym = {"lt": "<", "le": "<=", "gt": ">", "ge": ">=", "eq": "==", "ne": "!="}[op]
+            if x.dt != y.dt:
+                a, b = f"(float)({a})", f"(float)({b})"
+            return f"(({a}) {sym} ({b}) ? 1.0f : 0.0f)"
+        if e.dt == I32:
+            a, b = self.ex(x, lane), self.ex(y, lane)
+            if op in ("add", "sub", "mul"):
+                sym = {"add": "+", "sub": "-", "mul": "*"}[op]
+                return f"(int)((uint32_t)({a}) {sym} (uint32_t)({b}))"
+            return {"idiv": "anvil::idiv", "mod": "anvil::imod", "max": "anvil::imax", "min": "anvil::imin"}[op] + f"({a}, {b})"
+        a, b = self.cast(x, F32, lane), self.cast(y, F32, lane)
+        if op in ("add", "sub", "mul", "div"):
+            return f"(({a}) {dict(add='+', sub='-', mul='*', div='/')[op]} ({b}))"
+        return {"max": f"anvil::fmax_nan({a}, {b})", "min": f"anvil::fmin_nan({a}, {b})", "pow": f"powf({a}, {b})",
+                "idiv": f"floorf(({a}) / ({b}))", "mod": f"anvil::fmod_py({a}, {b})"}[op]
+
+    # ---- statements (anvil/backend/cuda.py:249-264)
+    def statements(self):
+        k = self.kg.k
+        L = self.lanes
+        for st in k.stmts:
+            if isinstance(st, kir.Let):
+                dep = self.depends(st.value)
+                d = {"dep": dep}
+                for lane in (range(L) if dep else [None]):
+                    v = self.ex(st.value, lane if lane is not None else 0)
+                    name = self.kg.tmp()
+                    self.emit(f"const {ctype(st.value.dt)} {name} = {v};")
+                    d[lane] = name
+                self.lets[st.id] = d
+                continue
+            self.store(st)
+            self.memo = {key: v for key, v in self.memo.items() if key[0] in ("sref",)}   # later loads re-read memory
+
+    def store(self, st: kir.Store):
+        k, L = self.kg.k, self.lanes
+        p = self.kg.ptr(st.buf, True)
+        dt = st.buf.dtype
+        vec_ok = (L == 4 and an.stride_of(st.offset, self.vv) == 1 and an.aligned4(st.offset, self.vv))
+        vals = [self.cast(st.value, dt, lane) for lane in range(L)]
+        exclusive = an.exclusive_store(k, st)
+        if vec_ok and (not st.accumulate or exclusive):
+            off = self.affine(st.offset, 0)
+            T4 = f"{ctype(dt)}4"
+            if st.accumulate:
+                q = self.kg.tmp("q")
+                self.emit(f"{T4} {q} = anvil::ld4({p} + ({off}));")
+                self.emit(f"{q}.x += {vals[0]}; {q}.y += {vals[1]}; {q}.z += {vals[2]}; {q}.w += {vals[3]};")
+                self.emit(f"anvil::st4({p} + ({off}), {q});")
+            else:
+                self.emit(f"anvil::st4({p} + ({off}), make_{T4}({', '.join(vals)}));")
+            return
+        for lane in range(L):
+            target = f"{p}[{self.affine(st.offset, lane)}]"
+            if st.accumulate:
+                if exclusive or not self.kg.parallel:
+                    self.emit(f"{target} += {vals[lane]};")
+                else:
+                    self.emit(f"atomicAdd(&{target}, {vals[lane]});")
+            else:
+                self.emit(f"{target} = {vals[lane]};")
+
+
+class KernelGen:
+    """One IR kernel -> one or two __global__ functions plus a host launcher."""
+
+    def __init__(self, gen: "ProgramGen", k: kir.Kernel):
+        self.gen = gen
+        self.k = k
+        self.n = 0
+        self.ptrs: dict = {}            # root id -> (buffer, written?)
+        self.parallel = an.parallel_safe(k)
+        self.dom = {v: f"d{i}" for i, v in enumerate(k.domain)}
+        self.red = {v: f"r{i}" for i, v in enumerate(k.red.vars)} if k.red else {}
+        self.names = {**self.dom, **self.red}
+        self.uses_rand = k.uses_rand()
+        self.written = {s.buf.root.id for s in k.stores}
+        self.strategy = ""
+        self.notes = ""
+
+    def tmp(self, prefix="t") -> str:
+        self.n += 1
+        return f"{prefix}{self.n}"
+
+    def ptr(self, b: kir.Buffer, write: bool) -> str:
+        r = b.root
+        w = r.id in self.written
+        self.ptrs[r.id] = (r, w)
+        return f"b{r.id}"
+
+    def rand_varies_with(self, vv) -> bool:
+        return vv in self.k.domain
+
+    def rand_index(self, scope: Scope, lane) -> str:
+        strides = kir.row_major_strides([v.extent for v in self.k.domain])
+        parts = [f"{s}u * (uint32_t){scope.var(v, lane)}" for v, s in zip(self.k.domain, strides)]
+        return " + ".join(parts) if parts else "0u"
+
+    def pointer_decls(self) -> list[str]:
+        out = []
+        for rid, (r, w) in sorted(self.ptrs.items()):
+            T = ctype(r.dtype)
+            off = self.gen.plan.offsets[rid]
+            if w:
+                out.append(f"    {T} *b{rid} = ({T} *)(A + {off}UL);   // {r.name}{list(r.shape)}")
+            else:
+                out.append(f"    const {T} *__restrict__ b{rid} = (const {T} *)(A + {off}UL);   // {r.name}{list(r.shape)}")
+        out.append("    anvil::Fault *fault_ = (anvil::Fault *)(A + ANVIL_RT_FAULT_OFF); (void)fault_;")
+        if self.uses_rand:
+            out.append("    const uint32_t stream_ = *(const uint32_t *)(A + ANVIL_RT_STREAM_OFF) + sdelta;")
+        return out
+
+    def head(self, name, threads) -> str:
+        return (f"__global__ void __launch_bounds__({threads}) {name}(char *__restrict__ A, uint32_t sdelta, "
+                f"uint32_t seed_) {{")
+
+    def comment(self, sched) -> str:
+        k = self.k
+        c = (f"// {k.name} | {k.label or 'kernel'} | {sched} | "
+             + " x ".join(f"{v.name}<{v.extent}" for v in k.domain))
+        if k.red is not None:
+            c += f"  {k.red.op} over " + " x ".join(f"{v.name}<{v.extent}" for v in k.red.vars)
+        return c
+
+    # ---- index decode
+    @staticmethod
+    def decode(src: str, vars_, names, ind, vec_var=None, L=1) -> list[str]:
+        """C lines that split the flat index `src` into `vars_` (row-major; the vectorised var counts
+        extent/L positions and is scaled by L)."""
+        ext = [(v.extent // L if v is vec_var else v.extent) for v in vars_]
+        strides = kir.row_major_strides(ext)
+        out = []
+        for v, st, n in zip(vars_, strides, ext):
+            idx = f"({src} / {st}u) % {n}u" if st != 1 else f"{src} % {n}u"
+            if st * n >= kir.prod(ext):
+                idx = f"{src} / {st}u" if st != 1 else src          # the outermost var needs no modulo
+            scale = f" * {L}" if (v is vec_var and L > 1) else ""
+            out.append(f"{ind}const int {names[v]} = (int)({idx}){scale};")
+        return out
+
+    def lane_vars(self, vv, L, ind) -> list[str]:
+        if L == 1:
+            return []
+        n = self.names[vv]
+        return [f"{ind}const int " + ", ".join(f"{n}_{l} = {n} + {l}" for l in range(L)) + ";"]
+
+    # ---- strategy choice
+    def choose(self):
+        k = self.k
+        ON, RN = k.out_numel(), k.red_numel()
+        if not self.parallel:
+            return ("serial",)
+        if k.red is None:
+            return ("eltwise", self.vec_width_domain())
+        if k.red.op in ("argmax", "argmin") or RN <= 64:
+            return ("thread",)
+        rlast = k.red.vars[-1]
+        dlast = k.domain[-1] if k.domain else None
+        row = col = 0
+        for n in k.red.body.walk():
+            if n.k == "load":
+                if an.stride_of(n.off, rlast) == 1:
+                    row += 1
+                if dlast is not None and an.stride_of(n.off, dlast) == 1:
+                    col += 1
+        if dlast is None or row > col or ON == 1:
+            L = self.vec_width_red()
+            RY = 256 if RN >= 2048 * max(1, L // 2) else 32
+            OX = THREADS // RY
+            layout = "row"
+        else:
+            L, OX, RY, layout = 1, 32, 8, "col"
+        blocks = (ON + OX - 1) // OX
+        S = 1
+        per_thread = RN // (RY * L)
+        if blocks < 148 and per_thread >= 64:
+            S = max(1, min(296 // blocks, per_thread // 32, 64))
+        return ("coop", layout, OX, RY, L, S)
+
+    def vec_width_domain(self) -> int:
+        k = self.k
+        if not k.domain:
+            return 1
+        vv = k.domain[-1]
+        if vv.extent % 4:
+            return 1
+        offs = list(k.offsets())
+        for a in offs:
+            st = an.stride_of(a, vv)
+            if st is None or st not in (0, 1):
+                return 1
+            if st == 1 and not an.aligned4(a, vv):
+                return 1
+        if not any(an.stride_of(s.offset, vv) == 1 for s in k.stores):
+            return 1
+        return 4
+
+    def vec_width_red(self) -> int:
+        k = self.k
+        vv = k.red.vars[-1]
+        if vv.extent % 4:
+            return 1
+        for n in k.red.body.walk():
+            if n.k in ("load", "index"):
+                for a in [n.off] + list(kir._nested(n.off)):
+                    st = an.stride_of(a, vv)
+                    if st is None or st not in (0, 1):
+                        return 1
+                    if st == 1 and not an.aligned4(a, vv):
+                        return 1
+        return 4
+
+    # ---- generation
+    def generate(self):
+        """Returns (device source, launcher body lines). The launcher receives `rt`, `A`, `st`
+        (stream), `sdelta`, `seed`."""
+        choice = self.choose()
+        self.strategy = choice[0]
+        base = f"k{self.k.id}"
+        if choice[0] == "serial":
+            return self.gen_serial(base)
+        if choice[0] == "eltwise":
+            return self.gen_eltwise(base, choice[1])
+        if choice[0] == "thread":
+            return self.gen_thread(base)
+        return self.gen_coop(base, *choice[1:])
+
+    def launch_line(self, name, blocks, threads) -> str:
+        return (f"{name}<<<{blocks}, {threads}, 0, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+
+    def gen_eltwise(self, base, L):
+        k = self.k
+        vv = k.domain[-1] if (L > 1 and k.domain) else None
+        NT = k.out_numel() // L
+        sc = Scope(self, self.names, L, vv)
+        sc.statements()
+        body = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {NT}L; tid += (long)gridDim.x * {THREADS}L) {{",
+                f"        const {index_t(NT)} u = ({index_t(NT)})tid;"]
+        body += self.decode("u", k.domain, self.names, "        ", vv, L)
+        body += self.lane_vars(vv, L, "        ") if vv is not None else []
+        src = [self.comment(f"elementwise, {L} element(s) per thread"), self.head(base, THREADS)]
+        src += self.pointer_decls() + body + sc.lines + ["    }", "}"]
+        blocks = max(1, min((NT + THREADS - 1) // THREADS, MAX_BLOCKS))
+        self.notes = f"eltwise x{L}"
+        return "\n".join(src), [self.launch_line(base, blocks, THREADS)]
+
+    def red_loops_serial(self, sc: Scope, ind: str) -> list[str]:
+        """acc over the whole reduction inside one thread (fixed row-major order)."""
+        red = self.k.red
+        T = ctype(red.body.dt)
+        out = []
+        arg = red.op in ("argmax", "argmin")
+        if arg:
+            init = ("-CUDART_INF_F" if red.op == "argmax" else "CUDART_INF_F") if red.body.dt == F32 else \
+                ("(-2147483647 - 1)" if red.op == "argmax" else "2147483647")
+            out.append(f"{ind}{T} best = {init}; int acc = 0; long ridx = 0;")
+        else:
+            out.append(f"{ind}{T} acc = {RED_OP[red.op]}::id<{T}>();")
+        inner = ind
+        for v in red.vars:
+            n = self.names[v]
+            out.append(f"{inner}for (int {n} = 0; {n} < {v.extent}; {n}++) {{")
+            inner += "    "
+        saved_lines, saved_memo, saved_ind = sc.lines, dict(sc.memo), sc.ind
+        sc.lines, sc.ind = [], inner
+        val = sc.ex(red.body, 0)
+        out += sc.lines
+        sc.lines, sc.memo, sc.ind = saved_lines, saved_memo, saved_ind
+        if arg:
+            cmp = ">" if red.op == "argmax" else "<"
+            out.append(f"{inner}if ({val} {cmp} best) {{ best = {val}; acc = (int)ridx; }}")
+            out.append(f"{inner}ridx++;")
+        else:
+            out.append(f"{inner}acc = {RED_OP[red.op]}::f(acc, {val});")
+        for _ in red.vars:
+            inner = inner[:-4]
+            out.append(f"{inner}}}")
+        return out
+
+    def gen_thread(self, base):
+        k = self.k
+        NT = k.out_numel()
+        sc = Scope(self, self.names)
+        red_lines = self.red_loops_serial(sc, "        ")
+        sc.statements()
+        body = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {NT}L; tid += (long)gridDim.x * {THREADS}L) {{",
+                f"        const {index_t(NT)} u = ({index_t(NT)})tid;"]
+        body += self.decode("u", k.domain, self.names, "        ")
+        src = [self.comment("reduction inside the thread"), self.head(base, THREADS)]
+        src += self.pointer_decls() + body + red_lines + sc.lines + ["    }", "}"]
+        blocks = max(1, min((NT + THREADS - 1) // THREADS, MAX_BLOCKS))
+        self.notes = "thread"
+        return "\n".join(src), [self.launch_line(base, blocks, THREADS)]
+
+    def gen_serial(self, base):
+        k = self.k
+        sc = Scope(self, self.names)
+        ind = "    "
+        lines = []
+        for v in k.domain:
+            lines.append(f"{ind}for (int {self.names[v]} = 0; {self.names[v]} < {v.extent}; {self.names[v]}++) {{")
+            ind += "    "
+        sc.ind = ind
+        if k.red is not None:
+            lines += self.red_loops_serial(sc, ind)
+        sc.statements()
+        lines += sc.lines
+        for _ in k.domain:
+            ind = ind[:-4]
+            lines.append(f"{ind}}}")
+        src = [self.comment("one thread (order-dependent)"), self.head(base, 1)] + self.pointer_decls() + lines + ["}"]
+        self.notes = "serial"
+        return "\n".join(src), [self.launch_line(base, 1, 1)]
+
+    def gen_coop(self, base, layout, OX, RY, L, S):
+        k = self.k
+        red = k.red
+        ON, RN = k.out_numel(), k.red_numel()
+        T = ctype(red.body.dt)
+        OP = RED_OP[red.op]
+        nthreads = OX * RY
+        vv = red.vars[-1] if L > 1 else None
+        RNL = RN // L                                    # reduction positions counted in lane groups
+        chunk = (RNL + S - 1) // S
+        ind = "    "
+        lines = []
+        if layout == "row":
+            lines.append(f"{ind}const int ry = threadIdx.x % {RY}, ox = threadIdx.x / {RY};")
+        else:
+            lines.append(f"{ind}const int ox = threadIdx.x % {OX}, ry = threadIdx.x / {OX};")
+        lines.append(f"{ind}const long o_ = blockIdx.x * {OX}L + ox;")
+        lines.append(f"{ind}const bool live = o_ < {ON}L;")
+        lines.append(f"{ind}const {index_t(ON)} u = ({index_t(ON)})(live ? o_ : {ON - 1}L);")
+        lines += self.decode("u", k.domain, self.names, ind)
+        lines.append(f"{ind}{T} acc = {OP}::id<{T}>();")
+        lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RNL}L, rbeg + {chunk}L);")
+        lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
+        inner = ind + "    "
+        lines.append(f"{inner}const {index_t(RNL)} rr = ({index_t(RNL)})rr_;")
+        lines += self.decode("rr", red.vars, self.names, inner, vv, L)
+        if vv is not None:
+            lines += self.lane_vars(vv, L, inner)
+        sc = Scope(self, self.names, L, vv, inner)
+        vals = [sc.ex(red.body, lane) for lane in range(L)] if sc.depends(red.body) or L == 1 else None
+        if vals is None:                                 # the body does not vary along the lanes
+            v0 = sc.ex(red.body, 0)
+            vals = [v0] * L
+        lines += sc.lines
+        for v in vals:
+            lines.append(f"{inner}acc = {OP}::f(acc, {v});")
+        lines.append(f"{ind}}}")
+        # combine across ry with a tree whose shape depends only on (layout, RY)
+        if layout == "row" and RY <= 32:
+            o = RY // 2
+            while o >= 1:
+                lines.append(f"{ind}acc = {OP}::f(acc, __shfl_xor_sync(0xffffffffu, acc, {o}));")
+                o //= 2
+        elif layout == "row":
+            lines.append(f"{ind}__shared__ {T} sm_[32];")
+            lines.append(f"{ind}acc = anvil::block_reduce<{OP}>(acc, sm_);")
+        else:
+            lines.append(f"{ind}__shared__ {T} sm_[{RY}][{OX + 1}];")
+            lines.append(f"{ind}sm_[ry][ox] = acc;")
+            lines.append(f"{ind}__syncthreads();")
+            s = RY // 2
+            while s >= 1:
+                lines.append(f"{ind}if (ry < {s}) sm_[ry][ox] = {OP}::f(sm_[ry][ox], sm_[ry + {s}][ox]);")
+                lines.append(f"{ind}__syncthreads();")
+                s //= 2
+            lines.append(f"{ind}acc = sm_[0][ox];")
+        tail = Scope(self, self.names, 1, None, ind + "    ")
+        launch = []
+        gx = (ON + OX - 1) // OX
+        if S == 1:
+            tail.statements()
+            lines.append(f"{ind}if (ry == 0 && live) {{")
+            lines += tail.lines
+            lines.append(f"{ind}}}")
+            src = [self.comment(f"cooperative reduction ({layout}, {OX} outputs x {RY} threads, {L} per load)"),
+                   self.head(base, nthreads)] + self.pointer_decls() + lines + ["}"]
+            launch.append(self.launch_line(base, f"dim3({gx}, 1)", nthreads))
+            self.notes = f"coop {layout} {OX}x{RY} L{L}"
+            return "\n".join(src), launch
+        # split: partial results to scratch, second kernel combines them in order and runs the statements
+        self.gen.need_scratch(4 * ON * S)
+        soff = self.gen.plan.scratch_off
+        lines.append(f"{ind}if (ry == 0 && live) (({T} *)(A + {soff}UL))[o_ * {S} + blockIdx.y] = acc;")
+        part = [self.comment(f"split reduction, part 1 of 2 ({layout}, {S} CTAs per output group)"),
+                self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
+        # final
+        saved = self.ptrs
+        self.ptrs = {}
+        fsc = Scope(self, self.names, 1, None, "        ")
+        fsc.statements()
+        fl = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {ON}L; tid += (long)gridDim.x * {THREADS}L) {{",
+              f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
+        fl += self.decode("u", k.domain, self.names, "        ")
+        fl.append(f"        {T} acc = {OP}::id<{T}>();")
+        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const {T} *)(A + {soff}UL))[tid * {S} + p]);")
+        final = [self.comment("split reduction, part 2 of 2"), self.head(base, THREADS)] + self.pointer_decls() \
+            + fl + fsc.lines + ["    }", "}"]
+        self.ptrs = {**saved, **self.ptrs}
+        launch.append(self.launch_line(base + "_part", f"dim3({gx}, {S})", nthreads))
+        fb = max(1, min((ON + THREADS - 1) // THREADS, MAX_BLOCKS))
+        launch.append(self.launch_line(base, fb, THREADS))
+        self.notes = f"split {layout} {OX}x{RY} L{L} S{S}"
+        return "\n".join(part) + "\n\n" + "\n".join(final), launch
+
+
+def index_t(n: int) -> str:
+    return "uint32_t" if n < (1 << 32) else "unsigned long long"
+
+
+class ProgramGen:
+    """Host side: the arena plan, one launcher per kernel, the program's control flow."""
+
+    def __init__(self, prog: kir.Program, seed: int = 0):
+        self.prog = prog
+        self.seed = seed & 0xFFFFFFFF
+        self.faults: list[str] = []
+        self.scratch_bytes = 4
+        self.plan = an.plan_arena(prog, 0)
+        self.kernel_index: dict[int, int] = {}
+        self.kernels: list[kir.Kernel] = []
+        self.kernel_src: list[str] = []
+        self.launchers: list[str] = []
+        self.kernel_notes: list[str] = []
+        self.tables: list[str] = []
+        self.n = 0
+        self.graph_keys = 0
+        self.hot = an.hot_loop(prog)
+        self.hot_body: list[str] | None = None
+        self.hot_counter = None
+
+    def fault(self, message: str) -> int:
+        if message in self.faults:
+            return self.faults.index(message) + 1
+        if len(self.faults) >= 254:
+            message = "index out of bounds"
+            if message in self.faults:
+                return self.faults.index(message) + 1
+        self.faults.append(message)
+        return len(self.faults)
+
+    def need_scratch(self, nbytes: int):
+        self.scratch_bytes = max(self.scratch_bytes, nbytes)
+
+    def label(self, hint: str) -> str:
+        self.n += 1
+        return f"{hint}{self.n}"
+
+    def off(self, b: kir.Buffer) -> str:
+        return f"{self.plan.off(b)}UL"
+
+    # ---- kernels
+    def add_kernel(self, k: kir.Kernel) -> int:
+        hit = self.kernel_index.get(k.id)
+        if hit is not None:
+            return hit
+        kg = KernelGen(self, k)
+        src, launch = kg.generate()
+        idx = len(self.kernels)
+        self.kernel_index[k.id] = idx
+        self.kernels.append(k)
+        self.kernel_src.append(src)
+        self.kernel_notes.append(kg.notes)
+        body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
+                "    uint32_t seed = anvil_rt_get_seed(rt);"]
+        body.append("    uint32_t sdelta = " + ("anvil_rt_next_stream_delta(rt);" if kg.uses_rand else "0;"))
+        body += ["    " + ln for ln in launch]
+        body.append("    return 0;")
+        self.launchers.append(f"static int launch_{idx}(anvil_rt *rt) {{   // {k.name} {k.label}\n" + "\n".join(body) + "\n}")
+        return idx
+
+    # ---- host control flow (anvil/backend/cuda.py:429-473)
+    def block(self, b: kir.Block, ind: str, in_loop: bool, tail: list[str] | None = None) -> list[str]:
+        """`tail`: host calls to issue right after the block's last statement (the loop counter
+        increment); they join the last launch run when the block ends with one."""
+        out = []
+        stmts = list(b.stmts)
+        i = 0
+        tail_done = False
+        while i < len(stmts):
+            st = stmts[i]
+            if isinstance(st, kir.KernelStmt):
+                j = i
+                run = []
+                while j < len(stmts) and isinstance(stmts[j], kir.KernelStmt):
+                    run.append(self.add_kernel(stmts[j].kernel))
+                    j += 1
+                calls = [f"RT(launch_{idx}(rt));" for idx in run]
+                if j == len(stmts) and tail is not None:
+                    calls += tail
+                    tail_done = True
+                if in_loop and len(calls) > 1:
+                    key = self.graph_keys
+                    self.graph_keys += 1
+                    out.append(f"{ind}{{ int g_ = anvil_rt_graph_begin(rt, {key}); if (g_ < 0) return 1;")
+                    out.append(f"{ind}  if (g_ != 0) {{")
+                    out += [f"{ind}    {c}" for c in calls]
+                    out.append(f"{ind}    if (g_ == 1) RT(anvil_rt_graph_end(rt, {key}));")
+                    out.append(f"{ind}  }} }}")
+                else:
+                    out += [f"{ind}{c}" for c in calls]
+                i = j
+                continue
+            out += self.stmt(st, ind, in_loop)
+            i += 1
+        if tail is not None and not tail_done:
+            out += [f"{ind}{c}" for c in tail]
+        return out
+
+    def read_scalar(self, b: kir.Buffer, var: str, ind: str) -> list[str]:
+        if b.dtype == I32:
+            return [f"{ind}int32_t {var}; RT(anvil_rt_read_i32(rt, {self.off(b)}, &{var}));"]
+        return [f"{ind}float {var}; RT(anvil_rt_read_f32(rt, {self.off(b)}, &{var}));"]
+
+    def stmt(self, st, ind: str, in_loop: bool) -> list[str]:
+        if isinstance(st, kir.For):
+            return self.for_(st, ind)
+        if isinstance(st, kir.While):
+            c = self.label("c")
+            out = [f"{ind}while (1) {{"] + self.block(st.cond_block, ind + "    ", True)
+            out += [f"{ind}    RT(anvil_rt_check_faults(rt));"] + self.read_scalar(st.cond, c, ind + "    ")
+            out += [f"{ind}    if ({c} == 0) break;"]
+            return out + self.block(st.body, ind + "    ", True) + [f"{ind}}}"]
+        if isinstance(st, kir.If):
+            c = self.label("c")
+            out = [f"{ind}{{", f"{ind}RT(anvil_rt_check_faults(rt));"] + self.read_scalar(st.cond, c, ind)
+            out += [f"{ind}if ({c} != 0) {{"] + self.block(st.then, ind + "    ", in_loop)
+            if st.orelse.stmts:
+                out += [f"{ind}}} else {{"] + self.block(st.orelse, ind + "    ", in_loop)
+            return out + [f"{ind}}}", f"{ind}}}"]
+        if isinstance(st, kir.Break):
+            return [f"{ind}break;"]
+        if isinstance(st, kir.Continue):
+            return [f"{ind}continue;"]
+        if isinstance(st, kir.Print):
+            return self.print_(st, ind)
+        if isinstance(st, kir.Check):
+            out = [f"{ind}{{ RT(anvil_rt_check_faults(rt)); long v_ = {st.value.const}L;"]
+            for t, c in st.value.terms:
+                if isinstance(t, kir.SRef):
+                    x = self.label("s")
+                    out += self.read_scalar(t.buf, x, ind + "  ")
+                    out.append(f"{ind}  v_ += {c}L * (long){x};")
+            out.append(f"{ind}  if (v_ < {st.lo}L || v_ > {st.hi}L) return anvil_rt_oob(rt, {c_string(st.message)}, v_); }}")
+            return out
+        if isinstance(st, kir.RTCall):
+            return [f"{ind}RT(anvil_rt_check_faults(rt));"] + [ind + ln for ln in self.rtcall(st)]
+        raise NotImplementedError(type(st).__name__)
+
+    def bound(self, x, var: str, ind: str) -> list[str]:
+        if isinstance(x, int):
+            return [f"{ind}long {var} = {x}L;"]
+        t = self.label("b")
+        return self.read_scalar(x, t, ind) + [f"{ind}long {var} = (long){t};"]
+
+    def for_(self, st: kir.For, ind: str) -> list[str]:
+        """The counter lives in the arena (kernels read it through scalar references); the host keeps
+        a mirror for the loop test and advances the device copy with a stream-ordered add."""
+        c = self.off(st.counter)
+        body_writes_counter = any(st.counter.root in s.kernel.writes() for b in kir.walk_blocks(st.body)
+                                  for s in b.stmts if isinstance(s, kir.KernelStmt))
+        has_continue = any(isinstance(s, kir.Continue) for b in kir.walk_blocks(st.body) for s in b.stmts)
+        lo, hi, i = self.label("lo"), self.label("hi"), self.label("i")
+        out = [f"{ind}{{"]
+        out += self.bound(st.start, lo, ind + "    ") + self.bound(st.stop, hi, ind + "    ")
+        out.append(f"{ind}    RT(anvil_rt_set_i32(rt, {c}, (int32_t){lo}));")
+        tail = [f"RT(anvil_rt_add_i32(rt, {c}, {st.step}));", "RT(anvil_rt_stream_commit(rt));"]
+        if body_writes_counter or has_continue:
+            out.append(f"{ind}    for (long {i} = {lo}; {i} < {hi}; ) {{")
+            out += self.block(st.body, ind + "        ", True)
+            out.append(f"{ind}        RT(anvil_rt_add_i32(rt, {c}, {st.step}));")
+            out += self.read_scalar(st.counter, i + "_", ind + "        ")
+            out.append(f"{ind}        {i} = {i}_;")
+            out.append(f"{ind}    }}")
+        else:
+            is_hot = st is self.hot and not any(isinstance(s, kir.Break) for b in kir.walk_blocks(st.body) for s in b.stmts)
+            body = self.block(st.body, ind + "        ", True, tail)
+            if is_hot:
+                self.hot_body = self.block(st.body, "    ", True, tail)
+                self.hot_counter = st.counter
+                out.append(f"{ind}    if (mode == 1) return 2;     // paused at the training loop")
+            out.append(f"{ind}    for (long {i} = {lo}; {i} < {hi}; {i} += {st.step}) {{")
+            out += body
+            out.append(f"{ind}    }}")
+        out.append(f"{ind}}}")
+        return out
+
+    def table(self, ctype_, items) -> str:
+        name = self.label("tab")
+        self.tables.append(f"static const {ctype_} {name}[] = {{{', '.join(items)}}};")
+        return name
+
+    def strings(self, strs) -> str:
+        return self.table("char *const", [c_string(s) for s in strs])
+
+    def print_(self, st: kir.Print, ind: str) -> list[str]:
+        err = 1 if st.err else 0
+        out = [f"{ind}RT(anvil_rt_check_faults(rt));"]
+        for it in list(st.items) + [kir.PrintItem("text", st.end)]:
+            if it.kind == "text":
+                if it.text:
+                    out.append(f"{ind}RT(anvil_rt_print_text(rt, {c_string(it.text)}, {err}));")
+            elif it.kind == "scalar":
+                isint = 1 if it.buf.dtype == I32 else 0
+                fint = 1 if (it.fmt and it.fmt.endswith("d")) else 0
+                out.append(f"{ind}RT(anvil_rt_print_scalar(rt, {self.off(it.buf)}, {isint}, {c_string(it.fmt or '')}, {fint}, {err}));")
+            elif it.kind == "tensor":
+                b = it.buf
+                dims = self.table("long", [str(d) for d in b.shape] or ["0"])
+                out.append(f"{ind}RT(anvil_rt_print_tensor(rt, {self.off(b)}, {1 if b.dtype == I32 else 0}, {len(b.shape)}, {dims}));")
+            elif it.kind == "pick":
+                out.append(f"{ind}RT(anvil_rt_print_pick(rt, {self.off(it.buf)}, {self.strings(it.choices)}, {len(it.choices)}, {err}));")
+            elif it.kind == "chars":
+                out.append(f"{ind}RT(anvil_rt_print_chars(rt, {self.off(it.buf)}, {it.buf.numel}L));")
+            else:
+                raise NotImplementedError(it.kind)
+        return out
+
+    def rtcall(self, st: kir.RTCall) -> list[str]:
+        a, n = st.args, st.name
+        b = a.get("buf")
+        if n == "seed":
+            return [f"anvil_rt_seed(rt, {a['value'] & 0xFFFFFFFF}u);"]
+        if n == "skip_rand":
+            return ["anvil_rt_set_stream(rt, anvil_rt_get_stream(rt) + 1u);"]
+        if n in ("iota", "iota_once"):
+            return [f"RT(anvil_rt_iota(rt, {self.off(b)}, {b.numel}L));"]
+        if n == "shuffle":
+            return [f"RT(anvil_rt_shuffle(rt, {self.off(b)}, {b.numel}L));"]
+        if n == "clock":
+            return [f"RT(anvil_rt_clock(rt, {self.off(b)}));"]
+        if n == "nonzero":
+            src = a["src"]
+            return [f"RT(anvil_rt_nonzero(rt, {self.off(src)}, {src.numel}L, {self.off(b)}, {b.numel}L));"]
+        if n == "show":
+            return [f"RT(anvil_rt_show(rt, {self.off(b)}, {a['rows']}L, {a['cols']}L, {self.strings(a['glyphs'])}, {len(a['glyphs'])}));"]
+        if n == "exit":
+            return ["anvil_rt_flush(rt);", f"return 1000 + ({int(a['value'])} & 255);"]
+        if n in ("save", "load"):
+            tab = self.label("ckpt")
+            entries = ", ".join(f"{{{self.off(x)}, {x.root.ckpt_key}ULL}}" for x in a["bufs"])
+            self.tables.append(f"static const anvil_rt_ckpt {tab}[] = {{{entries}}};")
+            if n == "save":
+                return [f"RT(anvil_rt_save(rt, {c_string(a['path'])}, {tab}, {len(a['bufs'])}L));"]
+            return [f"{{ float ok_; RT(anvil_rt_load(rt, {c_string(a['path'])}, {tab}, {len(a['bufs'])}L, &ok_)); "
+                    f"RT(anvil_rt_set_f32(rt, {self.off(b)}, ok_)); }}"]
+        if n == "save_npy":
+            tab = self.table("unsigned char", [str(x) for x in bytes(a["header"])])
+            return [f"RT(anvil_rt_save_npy(rt, {c_string(a['path'])}, {tab}, {len(a['header'])}L, {self.off(b)}, {4 * b.numel}L));"]
+        if n == "load_npy":
+            return [f"RT(anvil_rt_load_npy(rt, {c_string(a['path'])}, {self.off(b)}, {b.numel}L, {a['offset']}L, {a['kind']}, {a['size']}));"]
+        if n == "sleep":
+            return [f"{{ float s_; RT(anvil_rt_read_f32(rt, {self.off(b)}, &s_)); anvil_rt_flush(rt); "
+                    f"if (s_ > 0) usleep((useconds_t)(s_ * 1e6f)); }}"]
+        return [f"return anvil_rt_set_error(rt, \"anvil: runtime call `{n}` is not supported by the B200 back end\");"]
+
+    # ---- the translation unit
+    def generate(self) -> str:
+        main = self.block(self.prog.main, "    ", False)
+        # kernels that needed scratch were generated against scratch_off; re-plan with the final size
+        # (scratch sits before the buffers, so growing it moves every buffer: generate twice)
+        return self._assemble(main)
+
+    def _assemble(self, main) -> str:
+        externs = [b for b in self.prog.roots() if b.kind in ("input", "output")]
+        out = [f"// Generated by anvil-b200 from {self.prog.name}: sm_100a kernels over one device arena.",
+               "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
+               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', "",
+               "#define RT(call) do { if ((call) != 0) return 1; } while (0)", ""]
+        out += self.tables + [""]
+        out.append("static const char *const fault_messages[] = {\"\", " + ", ".join(c_string(m) for m in self.faults)
+                   + ("" if self.faults else "\"\"") + "};")
+        out += ["", "// ---------------------------------------------------------------- kernels"]
+        for src in self.kernel_src:
+            out += [src, ""]
+        out += ["// ---------------------------------------------------------------- launchers"]
+        out += self.launchers
+        n = len(self.kernels)
+        out += ["", "typedef int (*launch_fn)(anvil_rt *);",
+                "static const launch_fn launch_table[] = {" + ", ".join(f"launch_{i}" for i in range(n)) + ("0" if n == 0 else "") + "};",
+                f'extern "C" int anvil_b200_kernel_count(void) {{ return {n}; }}',
+                f'extern "C" unsigned long anvil_b200_arena_bytes(void) {{ return {self.plan.size}UL; }}',
+                f'extern "C" unsigned int anvil_b200_seed(void) {{ return {self.seed}u; }}',
+                'extern "C" int anvil_b200_launch(anvil_rt *rt, int idx) {',
+                f"    if (idx < 0 || idx >= {n}) return anvil_rt_set_error(rt, \"anvil: no such kernel\");",
+                "    return launch_table[idx](rt);", "}", ""]
+        out += ['extern "C" int anvil_b200_main(anvil_rt *rt, int mode) {',
+                f"    anvil_rt_fault_messages(rt, fault_messages, {len(self.faults) + 1});"]
+        out += main
+        out += ["    RT(anvil_rt_check_faults(rt));", "    anvil_rt_flush(rt);", "    return 0;", "}", ""]
+        out += ['extern "C" int anvil_b200_step(anvil_rt *rt) {   // one iteration of the training loop']
+        if self.hot_body is not None:
+            out += self.hot_body + ["    return 0;", "}"]
+        else:
+            out += ["    return anvil_rt_set_error(rt, \"anvil: the program has no training loop\");", "}"]
+        # anvil.function ABI (anvil/pyapi.py:237-299): pointer slots + anvil_entry, host arrays
+        if externs:
+            out += ["", "// ---------------------------------------------------------------- anvil.function entry"]
+            for b in externs:
+                out.append(f'extern "C" {{ void *anvil_{b.name} = 0; }}')
+            out += ['extern "C" { anvil_rt *anvil_b200_rt = 0; }',
+                    'extern "C" int anvil_entry(void) {', "    anvil_rt *rt = anvil_b200_rt;",
+                    "    if (!rt) return 1;", f"    anvil_rt_seed(rt, {self.seed}u);"]
+            for b in externs:
+                if b.kind == "input":
+                    out.append(f"    if (anvil_{b.name}) RT(anvil_rt_h2d_async(rt, {self.off(b)}, anvil_{b.name}, {max(b.nbytes, 4)}UL));")
+            out.append("    RT(anvil_b200_main(rt, 0));")
+            for b in externs:
+                if b.kind == "output":
+                    out.append(f"    if (anvil_{b.name}) RT(anvil_rt_d2h_async(rt, anvil_{b.name}, {self.off(b)}, {max(b.nbytes, 4)}UL));")
+            out += ["    return anvil_rt_sync(rt);", "}"]
+        return "\n".join(out) + "\n"
+
+
+def generate(prog: kir.Program, seed: int = 0):
+    """Returns (source text, ProgramGen). Generated twice when split reductions need scratch space,
+    because the scratch region sits in front of the buffers."""
+    g = ProgramGen(prog, seed)
+    src = g.generate()
+    if g.scratch_bytes > g.plan.scratch_bytes:
+        need = g.scratch_bytes
+        g = ProgramGen(prog, seed)
+        g.plan = an.plan_arena(prog, need)
+        g.scratch_bytes = need
+        src = g.generate()
+    return src, g

@@ -1,0 +1,83 @@
+"""`anvil run --cuda` on B200: the drop-in for the reference's CUDA back end module.
+
+Same entry points as anvil/backend/cuda.py:636-663 — `generate(prog, seed) -> str` and
+`build(source, exe, emulate)` raising `CudaToolchainError` — plus `run`, which is what
+`cli.build_cuda` + `subprocess.run([exe])` do in the reference (anvil/cli.py:127-136, 305-320).
+`prog` may be a live `anvil.ir.Program` (unmodified, straight from `driver.compile_file`) or an
+already converted `kir.Program`.
+
+Differences that follow from running in-process on a device arena: `build` produces a shared
+library, not an executable, and `emulate=True` is refused (there is no CPU path in this back end).
+"""
+from __future__ import annotations
+
+import sys
+
+from . import kir
+from .backend import build as _build
+from .backend import emit as _emit
+from .backend.build import CudaToolchainError  # noqa: F401  (part of the interface)
+from .program import AnvilRuntimeError, DeviceProgram  # noqa: F401
+
+
+def as_kir(prog, name: str = "<program>") -> kir.Program:
+    if isinstance(prog, kir.Program):
+        return prog
+    src = getattr(prog, "source", None)
+    if src is not None and hasattr(src, "display_path"):
+        name = src.display_path()
+    return kir.from_anvil(prog, name)
+
+
+def generate(prog, seed: int = 0) -> str:
+    """The program as one sm_100a CUDA C++ translation unit."""
+    return _emit.generate(as_kir(prog), seed)[0]
+
+
+def build(source: str, exe: str, emulate: bool = False):
+    """Compile generated source with nvcc for sm_100a into the shared library `exe`."""
+    if emulate:
+        raise CudaToolchainError("the B200 back end has no CPU emulation: run on a GPU, or use the "
+                                 "reference interpreter (`anvil run --interp`)")
+    _build.build_runtime()
+    _build.build_program(source, exe)
+
+
+def run(prog, seed: int = 0, capture: bool = False, device: int = 0, graphs: bool = True):
+    """Compile (cached) and execute on the device. Returns the exit status — 0, 1 after a run-time
+    error (message on stderr, as `anvil: runtime error: ...`), or the value of a failed `assert` —
+    and, with capture=True, the text the program printed."""
+    dp = DeviceProgram(as_kir(prog), seed=seed, device=device, graphs=graphs)
+    try:
+        code, text = dp.run(capture=capture)
+        if code == 1 and dp.error:
+            sys.stdout.flush()
+            print(dp.error, file=sys.stderr)
+        return (code, text) if capture else code
+    finally:
+        dp.close()
+
+
+def main(argv=None) -> int:
+    """`python -m anvil_lang_b200.cuda file.anvil [--seed N]` (needs the Anvil front end importable),
+    or `... file.kir.json[.gz]` for a program lowered elsewhere."""
+    import argparse
+    ap = argparse.ArgumentParser(prog="anvil-b200")
+    ap.add_argument("file")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--emit", action="store_true", help="print the generated CUDA instead of running")
+    ap.add_argument("--no-graphs", action="store_true")
+    args = ap.parse_args(argv)
+    if args.file.endswith((".json", ".json.gz")):
+        prog = kir.load(args.file)
+    else:
+        from anvil.driver import compile_file          # the reference front end
+        prog = as_kir(compile_file(args.file, seed=args.seed).program, args.file)
+    if args.emit:
+        print(generate(prog, args.seed))
+        return 0
+    return run(prog, seed=args.seed, graphs=not args.no_graphs)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,203 @@
+"""`anvil.function` on B200: NumPy arrays in, NumPy arrays out, computed on the GPU.
+
+Mirrors anvil/pyapi.py: `function(source, name, seed)` returns a `Function`; calling it with arrays
+picks (or compiles) the version for that combination of shapes (:76-81, signature rules :212-234:
+floats become f32, integers and bools i32, Python scalars and strings are compile-time constants).
+The per-shape lowering itself (`lower`, :114-181) is the reference front end's job and is used
+unchanged when the `anvil` package is importable. Where it is not, lowered programs are looked up
+in a directory of `.kir.json.gz` files keyed by (source, name, signature, seed) that `save_lowered`
+wrote on a machine that has the front end.
+
+`Compiled` replaces anvil/pyapi.py:237-299. The reference links AArch64 assembly into a library
+exporting `int anvil_entry(void)` and one `void *anvil_input{k}` / `anvil_output{k}` pointer slot
+per used argument; the library built here exports the same symbols with the same meaning (host
+pointers; the call copies inputs to the device arena, runs, and copies results back), so the
+calling code is the reference's: set slots, call the entry, clear slots, under a lock.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import threading
+
+import numpy as np
+
+from . import kir
+from .program import AnvilRuntimeError, DeviceProgram
+
+LOWERED_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "programs", "lowered")
+
+
+def arguments(args):
+    """NumPy arrays for the tensor arguments, and the signature that picks the compiled version."""
+    tensors, sig = [], []
+    for a in args:
+        if isinstance(a, (bool, int, float, str)) and not isinstance(a, np.generic):
+            if isinstance(a, bool):
+                text = "true" if a else "false"
+            elif isinstance(a, str):
+                text = f'"{a}"'
+            elif isinstance(a, float) and not np.isfinite(a):
+                text = "inf" if a > 0 else ("-inf" if a < 0 else "nan")
+            else:
+                text = repr(a)
+            sig.append(("const", text))
+            continue
+        arr = np.asarray(a)
+        if arr.dtype.kind == "f":
+            arr, dtype = np.ascontiguousarray(arr, dtype=np.float32), kir.F32
+        elif arr.dtype.kind in "iub":
+            arr, dtype = np.ascontiguousarray(arr, dtype=np.int32), kir.I32
+        else:
+            raise TypeError(f"anvil: cannot pass an array of {arr.dtype} (use floats or integers)")
+        tensors.append(arr)
+        sig.append(("tensor", tuple(int(d) for d in arr.shape), dtype))
+    return tensors, tuple(sig)
+
+
+def lowered_key(source: str, name: str, sig, seed: int) -> str:
+    return hashlib.sha256(repr((source, name, sig, seed)).encode()).hexdigest()[:20]
+
+
+class Lowered:
+    """A function as a program of its own (anvil/pyapi.py:101-111), in KIR."""
+
+    def __init__(self, prog: kir.Program, inputs, outputs, consts, tuple_result):
+        self.prog = prog
+        self.inputs = inputs          # kir buffers in argument order (tensor arguments only)
+        self.outputs = outputs        # kir buffers, None for a compile-time result
+        self.consts = consts
+        self.tuple_result = tuple_result
+
+
+def lower(source: str, path: str, name: str | None, sig, seed: int = 0) -> Lowered:
+    """Per-shape lowering through the reference front end, else from the shipped directory."""
+    try:
+        from anvil import pyapi as ref
+    except ImportError:
+        ref = None
+    if ref is not None:
+        if name is None:
+            name = ref.Function(source, seed=seed).name
+        lo = ref.lower(source if source.endswith("\n") else source + "\n", path, name, sig, seed=seed)
+        prog = kir.from_anvil(lo.prog, f"fn {name}")
+        by_id = {b.id: b for b in prog.buffers}
+        ins = [by_id[b.id] for b in lo.inputs]
+        outs = [None if b is None else by_id[b.id] for b in lo.outputs]
+        return Lowered(prog, ins, outs, list(lo.consts), lo.tuple_result)
+    f = os.path.join(LOWERED_DIR, lowered_key(source, name or "", sig, seed) + ".kir.json.gz")
+    if not os.path.exists(f):
+        raise AnvilRuntimeError("anvil: the Anvil front end is not importable and no lowered program is stored for "
+                                f"this source and signature ({f})")
+    return load_lowered(f)
+
+
+def save_lowered(lo: Lowered, path: str):
+    import gzip
+    import json
+    meta = {"inputs": [b.id for b in lo.inputs], "outputs": [None if b is None else b.id for b in lo.outputs],
+            "consts": lo.consts, "tuple": lo.tuple_result, "kir": kir.dumps(lo.prog)}
+    with gzip.GzipFile(path, "wb", mtime=0) as f:
+        f.write(json.dumps(meta).encode())
+
+
+def load_lowered(path: str) -> Lowered:
+    import gzip
+    import json
+    with gzip.open(path, "rb") as f:
+        meta = json.loads(f.read().decode())
+    prog = kir.loads(meta["kir"])
+    by_id = {b.id: b for b in prog.buffers}
+    return Lowered(prog, [by_id[i] for i in meta["inputs"]], [None if i is None else by_id[i] for i in meta["outputs"]],
+                   meta["consts"], meta["tuple"])
+
+
+class Compiled:
+    """One version of a Function: a GPU library for one combination of argument shapes."""
+
+    def __init__(self, name, lowered: Lowered, seed: int, device: int = 0):
+        self.name = name
+        self.lowered = lowered
+        self.prog = lowered.prog
+        self.inputs = lowered.inputs
+        self.outputs = lowered.outputs
+        self.consts = lowered.consts
+        self.tuple_result = lowered.tuple_result
+        self.dp = DeviceProgram(self.prog, seed=seed, device=device, graphs=False)
+        self.lib = self.dp.lib
+        ctypes.c_void_p.in_dll(self.lib, "anvil_b200_rt").value = self.dp.rt
+        self.entry = self.lib.anvil_entry
+        self.entry.restype = ctypes.c_int
+        self.entry.argtypes = []
+        used = {r.id for r in self.prog.roots()}
+
+        def slot(b):
+            if b is None or b.root.id not in used:
+                return None
+            try:
+                return ctypes.c_void_p.in_dll(self.lib, f"anvil_{b.name}")
+            except ValueError:
+                return None
+        self.in_slots = [slot(b) for b in self.inputs]
+        self.out_slots = [slot(b) for b in self.outputs]
+        self.lock = threading.Lock()
+
+    def call(self, arrays):
+        results = [None if b is None else np.empty(b.shape, np.float32 if b.dtype == kir.F32 else np.int32)
+                   for b in self.outputs]
+        with self.lock:
+            for s, a in zip(self.in_slots, arrays):
+                if s is not None:
+                    s.value = a.ctypes.data
+            for s, r in zip(self.out_slots, results):
+                if s is not None:
+                    s.value = r.ctypes.data
+            rc = self.entry()
+            for s in self.in_slots + self.out_slots:
+                if s is not None:
+                    s.value = None
+        if rc != 0:
+            raise AnvilRuntimeError(self.dp.rtlib.anvil_rt_last_error(self.dp.rt).decode("utf-8", "replace"))
+        consts = iter(self.consts)
+        out = [next(consts) if r is None else (r[()] if r.ndim == 0 else r) for r in results]
+        return tuple(out) if self.tuple_result else out[0]
+
+    # device-resident calls: inputs already in the arena, results left there
+    def run_resident(self):
+        self.dp._check(self.lib.anvil_b200_main(self.dp.rt, 0))
+
+
+class Function:
+    """An Anvil function callable from Python on a B200 (anvil/pyapi.py:46-94)."""
+
+    def __init__(self, source: str, name: str | None = None, seed: int = 0, device: int = 0):
+        if "\n" not in source and source.endswith(".anvil") and os.path.exists(source):
+            self.path = os.path.abspath(source)
+            with open(source, encoding="utf-8") as f:
+                source = f.read()
+        else:
+            self.path = os.path.join(os.getcwd(), "<python>.anvil")
+        self.source = source if source.endswith("\n") else source + "\n"
+        self.name = name
+        self.seed = seed
+        self.device = device
+        self.versions: dict[tuple, Compiled] = {}
+
+    def __call__(self, *args):
+        tensors, sig = arguments(args)
+        return self.lower_sig(sig).call(tensors)
+
+    def lower(self, *args) -> Compiled:
+        return self.lower_sig(arguments(args)[1])
+
+    def lower_sig(self, sig) -> Compiled:
+        fn = self.versions.get(sig)
+        if fn is None:
+            lo = lower(self.source, self.path, self.name, sig, seed=self.seed)
+            fn = self.versions[sig] = Compiled(self.name, lo, seed=self.seed, device=self.device)
+        return fn
+
+
+def function(source: str, name: str | None = None, seed: int = 0) -> Function:
+    return Function(source, name=name, seed=seed)

@@ -1,0 +1,128 @@
+/* anvil_cuda.h — C ABI of libanvil_cuda.so, the B200 runtime for Anvil programs.
+ *
+ * The library replaces the two runtime headers that the reference pastes into every generated
+ * .cu file (anvil/backend/anvil_cuda.h and anvil/backend/anvil_host.h). Where the reference keeps
+ * every tensor in CUDA unified memory and synchronises the device before each host touch, this
+ * runtime owns ONE cudaMalloc'd arena per context; the host never dereferences device pointers and
+ * every host-side service (printing, shuffle, checkpoints, loaders) moves data with explicit copies
+ * on the context's stream.
+ *
+ * Conventions: plain pointers and sizes only; every function that can fail returns 0 on success and
+ * a non-zero status otherwise, with the text available from anvil_rt_last_error(); nothing in the
+ * library calls exit(). Offsets are byte offsets into the arena. One host thread per context.
+ *
+ * Arena layout: bytes [0, ANVIL_RT_HEADER_BYTES) are the header (fault record, device copy of the
+ * random stream counter, spare words); program buffers follow at offsets chosen by the compiler's
+ * arena plan.
+ */
+#ifndef ANVIL_CUDA_H
+#define ANVIL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ANVIL_RT_HEADER_BYTES 256
+#define ANVIL_RT_FAULT_OFF 0        /* struct { int code; int pad; long long value; }            */
+#define ANVIL_RT_STREAM_OFF 16      /* uint32: device copy of the random stream counter           */
+#define ANVIL_RT_STATUS_OFF 32      /* uint32: status word written by kernels that give up a wait */
+
+typedef struct anvil_rt anvil_rt;
+
+/* ---- context and arena ------------------------------------------------------------------------
+ * Replaces the per-tensor anvil_alloc / cudaMallocManaged + memset of the reference
+ * (anvil/backend/anvil_cuda.h:42-46, 82-87): one zero-filled allocation for the whole program. */
+anvil_rt *anvil_rt_create(int device);
+void anvil_rt_destroy(anvil_rt *rt);
+int anvil_rt_arena(anvil_rt *rt, size_t bytes);
+void *anvil_rt_ptr(anvil_rt *rt, size_t off);                 /* device address of an arena offset */
+size_t anvil_rt_arena_bytes(anvil_rt *rt);
+void *anvil_rt_stream(anvil_rt *rt);                          /* the context's cudaStream_t        */
+int anvil_rt_use_stream(anvil_rt *rt, void *cuda_stream);     /* run on a caller-owned stream      */
+const char *anvil_rt_last_error(anvil_rt *rt);
+int anvil_rt_set_error(anvil_rt *rt, const char *message);    /* returns 1                         */
+
+/* ---- data movement (replaces direct host access to unified memory) ---------------------------- */
+int anvil_rt_h2d(anvil_rt *rt, size_t off, const void *src, size_t bytes);   /* synchronous         */
+int anvil_rt_d2h(anvil_rt *rt, void *dst, size_t off, size_t bytes);         /* synchronous         */
+int anvil_rt_h2d_async(anvil_rt *rt, size_t off, const void *pinned_src, size_t bytes);
+int anvil_rt_d2h_async(anvil_rt *rt, void *pinned_dst, size_t off, size_t bytes);
+int anvil_rt_zero(anvil_rt *rt, size_t off, size_t bytes);
+int anvil_rt_sync(anvil_rt *rt);                              /* anvil_sync, anvil_cuda.h:55-58    */
+void *anvil_rt_host_alloc(size_t bytes);                      /* pinned host memory                */
+void anvil_rt_host_free(void *p);
+
+/* ---- scalars that host control flow reads or writes ---------------------------------------------
+ * Loop counters and conditions are i32/f32 0-d buffers in the arena (reference: `b[0]` on unified
+ * memory, anvil/backend/cuda.py:435-456). Writes are stream-ordered kernels; reads synchronise. */
+int anvil_rt_set_i32(anvil_rt *rt, size_t off, int32_t value);
+int anvil_rt_set_f32(anvil_rt *rt, size_t off, float value);
+int anvil_rt_add_i32(anvil_rt *rt, size_t off, int32_t delta);
+int anvil_rt_read_i32(anvil_rt *rt, size_t off, int32_t *out);
+int anvil_rt_read_f32(anvil_rt *rt, size_t off, float *out);
+
+/* ---- random numbers -----------------------------------------------------------------------------
+ * The counter hash of anvil/backend/anvil_host.h:17-29. A kernel that draws random numbers takes
+ * the next stream number (anvil/backend/cuda.py:490-494). The host counter is authoritative; the
+ * device copy in the header lets captured launch sequences be replayed: a launch passes
+ * `delta = host counter - device copy` and the kernel uses `device copy + delta`. */
+void anvil_rt_seed(anvil_rt *rt, uint32_t seed);              /* sets the seed, stream counter = 0 */
+uint32_t anvil_rt_get_seed(anvil_rt *rt);
+uint32_t anvil_rt_get_stream(anvil_rt *rt);
+void anvil_rt_set_stream(anvil_rt *rt, uint32_t stream);
+uint32_t anvil_rt_next_stream_delta(anvil_rt *rt);            /* takes a stream number; returns delta */
+int anvil_rt_stream_commit(anvil_rt *rt);                     /* device copy += pending; delta -> 0 */
+uint32_t anvil_rt_rand_bits(uint32_t idx, uint32_t stream, uint32_t salt, uint32_t seed);
+float anvil_rt_rand(uint32_t idx, uint32_t stream, uint32_t salt, uint32_t seed, int open_low);
+
+/* ---- runtime calls of the IR (anvil/backend/cuda.py:551-594; anvil_host.h:237-284) ------------ */
+int anvil_rt_iota(anvil_rt *rt, size_t off, long n);
+int anvil_rt_shuffle(anvil_rt *rt, size_t off, long n);       /* Fisher-Yates, anvil_host.h:269-276 */
+int anvil_rt_nonzero(anvil_rt *rt, size_t src_off, long n, size_t dst_off, long size);
+int anvil_rt_clock(anvil_rt *rt, size_t off);                 /* seconds since create, after a sync */
+typedef struct { size_t off; uint64_t key; } anvil_rt_ckpt;  /* key: ir.ckpt_key                   */
+int anvil_rt_save(anvil_rt *rt, const char *path, const anvil_rt_ckpt *tab, long n);
+int anvil_rt_load(anvil_rt *rt, const char *path, const anvil_rt_ckpt *tab, long n, float *ok);
+int anvil_rt_save_npy(anvil_rt *rt, const char *path, const unsigned char *header, long hlen,
+                      size_t off, long bytes);
+int anvil_rt_load_npy(anvil_rt *rt, const char *path, size_t off, long n, long offset, int kind, int size);
+
+/* ---- output (anvil_host.h:76-132) ----------------------------------------------------------------
+ * Text goes to stdout/stderr, or into a capture buffer when capture is on (tests, notebooks). */
+int anvil_rt_capture(anvil_rt *rt, int on);
+const char *anvil_rt_captured(anvil_rt *rt);                  /* text so far; valid until next call */
+int anvil_rt_print_text(anvil_rt *rt, const char *text, int to_stderr);
+int anvil_rt_print_scalar(anvil_rt *rt, size_t off, int is_int, const char *fmt, int fmt_is_int, int to_stderr);
+int anvil_rt_print_tensor(anvil_rt *rt, size_t off, int is_int, int rank, const long *dims);
+int anvil_rt_print_pick(anvil_rt *rt, size_t off, const char *const *choices, int n, int to_stderr);
+int anvil_rt_print_chars(anvil_rt *rt, size_t off, long n);
+int anvil_rt_show(anvil_rt *rt, size_t off, long rows, long cols, const char *const *glyphs, int n);
+int anvil_rt_flush(anvil_rt *rt);
+
+/* ---- faults (anvil/backend/anvil_cuda.h:66-103) --------------------------------------------------
+ * A failed gather bounds check inside a kernel records the first {code, value} in the header and
+ * clamps the index; nothing traps. anvil_rt_check_faults synchronises, and on a fault returns 1
+ * with last_error = "anvil: runtime error: <message> (got <value>)". */
+int anvil_rt_fault_messages(anvil_rt *rt, const char *const *messages, int n);
+int anvil_rt_check_faults(anvil_rt *rt);
+int anvil_rt_oob(anvil_rt *rt, const char *message, long long value);   /* anvil_oob, anvil_host.h:69-73 */
+
+/* ---- launch-sequence capture (no reference counterpart: the reference synchronises the device at
+ * every loop iteration, anvil/backend/cuda.py:443-445). A run of kernel launches inside a loop body
+ * is recorded once into a CUDA graph keyed by `key` and replayed on later iterations. */
+int anvil_rt_graph_begin(anvil_rt *rt, int key);   /* 0: replayed a cached graph (skip the launches)
+                                                     1: capturing now, issue the launches then _end
+                                                     2: graphs are off, issue the launches, no _end
+                                                    <0: error */
+int anvil_rt_graph_end(anvil_rt *rt, int key);
+void anvil_rt_graphs(anvil_rt *rt, int on);
+long anvil_rt_launch_count(anvil_rt *rt);          /* kernels launched (graph replays count their nodes) */
+void anvil_rt_count_launches(anvil_rt *rt, long n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
