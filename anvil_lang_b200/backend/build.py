@@ -130,6 +130,8 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_print_text": (I, [P, c.c_char_p, I]), "anvil_rt_flush": (I, [P]),
         "anvil_rt_check_faults": (I, [P]),
         "anvil_rt_graphs": (None, [P, I]), "anvil_rt_launch_count": (L, [P]),
+        "anvil_rt_timer_begin": (I, [P]), "anvil_rt_timer_end": (I, [P, c.POINTER(c.c_float)]),
+        "anvil_rt_time_launch": (I, [P, P, I, I, c.POINTER(c.c_float)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

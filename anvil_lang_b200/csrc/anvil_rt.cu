@@ -45,6 +45,7 @@ struct anvil_rt {
     uint32_t capture_stream0 = 0;
     std::map<int, anvil_graph> graphs;
     long launches = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
 };
 
 static double now_seconds() {
@@ -92,6 +93,7 @@ extern "C" void anvil_rt_destroy(anvil_rt *rt) {
     if (rt->stream) cudaStreamSynchronize(rt->stream);
     for (auto &g : rt->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     if (rt->arena) cudaFree(rt->arena);
+    if (rt->ev0) { cudaEventDestroy(rt->ev0); cudaEventDestroy(rt->ev1); }
     if (rt->stream && rt->own_stream) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -550,5 +552,40 @@ extern "C" int anvil_rt_graph_end(anvil_rt *rt, int key) {
     rt->graphs[key] = rec;
     (void)before;
     CK(rt, cudaGraphLaunch(rec.exec, rt->stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------- device timing
+static int ensure_events(anvil_rt *rt) {
+    if (!rt->ev0) { CK(rt, cudaEventCreate(&rt->ev0)); CK(rt, cudaEventCreate(&rt->ev1)); }
+    return 0;
+}
+extern "C" int anvil_rt_timer_begin(anvil_rt *rt) {
+    if (ensure_events(rt)) return 1;
+    CK(rt, cudaEventRecord(rt->ev0, rt->stream));
+    return 0;
+}
+extern "C" int anvil_rt_timer_end(anvil_rt *rt, float *ms) {
+    if (ensure_events(rt)) return 1;
+    CK(rt, cudaEventRecord(rt->ev1, rt->stream));
+    CK(rt, cudaEventSynchronize(rt->ev1));
+    CK(rt, cudaEventElapsedTime(ms, rt->ev0, rt->ev1));
+    return 0;
+}
+extern "C" int anvil_rt_time_launch(anvil_rt *rt, anvil_launch_fn launch, int index, int repeats, float *ms) {
+    if (ensure_events(rt)) return 1;
+    if (repeats < 1) repeats = 1;
+    uint32_t stream0 = rt->host_stream, pending0 = rt->pending;
+    CK(rt, cudaStreamSynchronize(rt->stream));
+    CK(rt, cudaEventRecord(rt->ev0, rt->stream));
+    for (int i = 0; i < repeats; i++) {
+        rt->host_stream = stream0; rt->pending = pending0;      // every repeat draws the same numbers
+        if (launch(rt, index)) return 1;
+    }
+    CK(rt, cudaEventRecord(rt->ev1, rt->stream));
+    CK(rt, cudaEventSynchronize(rt->ev1));
+    float total = 0;
+    CK(rt, cudaEventElapsedTime(&total, rt->ev0, rt->ev1));
+    *ms = total / repeats;
     return 0;
 }

@@ -121,6 +121,23 @@ class DeviceProgram:
     def check_faults(self):
         self._check(self.rtlib.anvil_rt_check_faults(self.rt))
 
+    def timer_begin(self):
+        self._check(self.rtlib.anvil_rt_timer_begin(self.rt))
+
+    def timer_end(self) -> float:
+        """Milliseconds on the device since `timer_begin` (CUDA events on the program's stream)."""
+        ms = ctypes.c_float()
+        self._check(self.rtlib.anvil_rt_timer_end(self.rt, ctypes.byref(ms)))
+        return float(ms.value)
+
+    def time_kernel(self, kernel, repeats: int = 1) -> float:
+        """Mean device milliseconds of one kernel's launcher (all its passes), timed alone."""
+        idx = kernel if isinstance(kernel, int) else self.gen.kernel_index[kernel.id]
+        ms = ctypes.c_float()
+        fn = ctypes.cast(self.lib.anvil_b200_launch, ctypes.c_void_p)
+        self._check(self.rtlib.anvil_rt_time_launch(self.rt, fn, idx, repeats, ctypes.byref(ms)))
+        return float(ms.value)
+
     @property
     def launches(self) -> int:
         return int(self.rtlib.anvil_rt_launch_count(self.rt))

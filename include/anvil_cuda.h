@@ -122,6 +122,15 @@ void anvil_rt_graphs(anvil_rt *rt, int on);
 long anvil_rt_launch_count(anvil_rt *rt);          /* kernels launched (graph replays count their nodes) */
 void anvil_rt_count_launches(anvil_rt *rt, long n);
 
+/* ---- device timing (no reference counterpart; the reference's `--profile` reads a CPU counter
+ * around every kernel call, anvil/backend/aarch64.py:382-402). CUDA events on the context's stream. */
+int anvil_rt_timer_begin(anvil_rt *rt);
+int anvil_rt_timer_end(anvil_rt *rt, float *milliseconds);    /* synchronises on the end event   */
+/* Times ONE call of a program's kernel launcher (`launch(rt, index)` as exported by a generated
+ * library) `repeats` times back to back and returns the mean milliseconds per call. */
+typedef int (*anvil_launch_fn)(anvil_rt *, int);
+int anvil_rt_time_launch(anvil_rt *rt, anvil_launch_fn launch, int index, int repeats, float *milliseconds);
+
 #ifdef __cplusplus
 }
 #endif
