@@ -146,3 +146,44 @@ def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256) -> 
         offsets[r.id] = pos
         pos += up(max(r.nbytes, 16))
     return ArenaPlan(offsets, pos, scratch_off, up(max(scratch_bytes, 4)))
+
+
+# ----------------------------------------------------------------------------- algorithmic work
+FREE_UNARY = ("detach", "f32", "i32")
+
+
+def kernel_flops(k: kir.Kernel) -> int:
+    """Arithmetic of one kernel execution as the reference's cost model counts it
+    (anvil/cost.py:22-37): every binary op, select and non-free unary op is 1, a reduction adds one
+    accumulation per reduced element (so a multiply-add is 2)."""
+    def ops(e: kir.E) -> int:
+        seen, n = set(), 0
+        stack = [e]
+        while stack:
+            x = stack.pop()
+            if x.k in ("bin", "sel") or (x.k == "un" and x.op not in FREE_UNARY):
+                n += 1
+            stack.extend(x.a)
+        return n
+    per = 0
+    if k.red is not None:
+        per += k.red_numel() * (ops(k.red.body) + 1)
+    per += sum(ops(st.value) for st in k.stmts)
+    return k.out_numel() * per
+
+
+def kernel_bytes(k: kir.Kernel) -> int:
+    """Compulsory memory traffic of one kernel execution (anvil/cost.py:40-52): each tensor read
+    counts once, but no more elements than its loads can reach; each store writes the domain once."""
+    dom, red = k.out_numel(), k.red_numel()
+    reach: dict = {}
+    parts = ([(k.red.body, dom * red)] if k.red is not None else []) + [(st.value, dom) for st in k.stmts]
+    roots = {}
+    for e, n in parts:
+        for x in e.walk():
+            if x.k == "load":
+                r = x.buf.root
+                roots[r.id] = r
+                reach[r.id] = reach.get(r.id, 0) + n
+    read = sum(4 * min(roots[i].numel, n) for i, n in reach.items())
+    return read + 4 * dom * len(k.stores)

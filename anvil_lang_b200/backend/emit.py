@@ -31,6 +31,7 @@ import math
 from .. import kir
 from ..kir import F32, I32
 from . import analysis as an
+from . import contraction as ct
 
 THREADS = 256
 MAX_BLOCKS = 148 * 8
@@ -402,6 +403,9 @@ class KernelGen:
             return ("serial",)
         if k.red is None:
             return ("eltwise", self.vec_width_domain())
+        c = ct.match(k)
+        if c is not None:
+            return ("gemm", c)
         if k.red.op in ("argmax", "argmin") or RN <= 64:
             return ("thread",)
         rlast = k.red.vars[-1]
@@ -473,6 +477,8 @@ class KernelGen:
             return self.gen_eltwise(base, choice[1])
         if choice[0] == "thread":
             return self.gen_thread(base)
+        if choice[0] == "gemm":
+            return self.gen_gemm(base, choice[1])
         return self.gen_coop(base, *choice[1:])
 
     def launch_line(self, name, blocks, threads) -> str:
@@ -655,6 +661,66 @@ class KernelGen:
         launch.append(self.launch_line(base, fb, THREADS))
         self.notes = f"split {layout} {OX}x{RY} L{L} S{S}"
         return "\n".join(part) + "\n\n" + "\n".join(final), launch
+
+
+    # ---- contractions
+    def functor_method(self, sig: str, decodes: list, build) -> list[str]:
+        """One __device__ method of a contraction functor: index decode, pointers, body."""
+        saved = self.ptrs
+        self.ptrs = {}
+        sc = Scope(self, self.names, 1, None, "        ")
+        ret = build(sc)
+        decls = ["    " + ln for ln in self.pointer_decls()]
+        out = [f"    __device__ __forceinline__ {sig} const {{"] + decls + decodes + sc.lines
+        if ret is not None:
+            out.append(f"        return {ret};")
+        out.append("    }")
+        self.ptrs = {**saved, **self.ptrs}
+        return out
+
+    def gen_gemm(self, base, c):
+        k = self.k
+        M, N, K, NB = c.M, c.N, c.K, c.NB
+        ind = "        "
+        dm = self.decode("(uint32_t)m", c.mvars, self.names, ind)
+        dn = self.decode("(uint32_t)n", c.nvars, self.names, ind)
+        dk = self.decode("(uint32_t)k", c.kvars, self.names, ind)
+        db = self.decode("(uint32_t)bt", c.bvars, self.names, ind) if c.bvars else []
+        fa = self.functor_method("float a(int m, int k, int bt)", dm + dk + db, lambda sc: sc.ex(c.a, 0))
+        fb = self.functor_method("float b(int k, int n, int bt)", dk + dn + db, lambda sc: sc.ex(c.b, 0))
+
+        def epi(sc):
+            sc.statements()
+            return None
+        fe = self.functor_method("void epi(int m, int n, int bt, float acc)", dm + dn + db, epi)
+        tiles = ((M + 127) // 128) * ((N + 127) // 128)
+        S = 1
+        if tiles * NB < 148 and K >= 256:
+            S = max(1, min(296 // (tiles * NB), K // 128, 32))
+        AK, BNC = ("true" if c.a_kcontig else "false"), ("true" if c.b_ncontig else "false")
+        fn = f"G{k.id}"
+        src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (CUDA-core tiles, split {S})"),
+               f"struct {fn} {{", "    char *__restrict__ A;",
+               f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = {NB};",
+               f"    static constexpr float ALPHA = {flit(c.alpha)};"] + fa + fb + fe + ["};"]
+        launch = []
+        if S == 1:
+            src += [f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                    f"    anvil::gemm_simt_tile<{fn}, {AK}, {BNC}, 1>({fn}{{A}}, nullptr);", "}"]
+            launch.append(self.launch_line(base, f"dim3({tiles}, {NB})", 256))
+        else:
+            self.gen.need_scratch(4 * M * N * NB * S)
+            soff = self.gen.plan.scratch_off
+            src += [f"__global__ void __launch_bounds__(256) {base}_part(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                    f"    anvil::gemm_simt_tile<{fn}, {AK}, {BNC}, {S}>({fn}{{A}}, (float *)(A + {soff}UL));", "}",
+                    f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                    f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
+            launch.append(self.launch_line(base + "_part", f"dim3({tiles}, {NB * S})", 256))
+            fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
+            launch.append(self.launch_line(base, fb_, 256))
+        self.notes = f"gemm simt {NB}x{M}x{N}x{K} S{S}"
+        self.contraction = c
+        return "\n".join(src), launch
 
 
 def index_t(n: int) -> str:
@@ -918,7 +984,7 @@ class ProgramGen:
         externs = [b for b in self.prog.roots() if b.kind in ("input", "output")]
         out = [f"// Generated by anvil-b200 from {self.prog.name}: sm_100a kernels over one device arena.",
                "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
-               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', "",
+               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', "",
                "#define RT(call) do { if ((call) != 0) return 1; } while (0)", ""]
         out += self.tables + [""]
         out.append("static const char *const fault_messages[] = {\"\", " + ", ".join(c_string(m) for m in self.faults)
