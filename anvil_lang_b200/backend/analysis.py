@@ -187,3 +187,32 @@ def kernel_bytes(k: kir.Kernel) -> int:
                 reach[r.id] = reach.get(r.id, 0) + n
     read = sum(4 * min(roots[i].numel, n) for i, n in reach.items())
     return read + 4 * dom * len(k.stores)
+
+
+def input_producers(prog: kir.Program, hot: kir.For):
+    """The kernels at the head of the training loop that only produce the step's inputs: a batch
+    gathered out of resident data through the shuffled permutation, or freshly sampled tokens.
+    A caller that feeds batches from host memory copies into the buffers they write and skips them.
+    Returns (kernels, buffers they write)."""
+    ks, bufs = [], []
+    if hot is None:
+        return ks, bufs
+    written_in_loop = set()
+    for b in kir.walk_blocks(hot.body):
+        for st in b.stmts:
+            if isinstance(st, kir.KernelStmt):
+                written_in_loop |= {r.id for r in st.kernel.writes()}
+    for st in hot.body.stmts:
+        if not isinstance(st, kir.KernelStmt):
+            break
+        k = st.kernel
+        if k.red is not None or any(s.accumulate for s in k.stores):
+            break
+        reads = k.reads()
+        if any(r.id in written_in_loop for r in reads):
+            break                                    # depends on something the step computes
+        if not k.uses_rand() and not any(r.numel > 1 for r in reads):
+            break                                    # a constant fill, not an input
+        ks.append(k)
+        bufs += [s.buf.root for s in k.stores]
+    return ks, bufs

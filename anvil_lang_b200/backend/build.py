@@ -155,4 +155,6 @@ def load_program(path: str) -> ctypes.CDLL:
     lib.anvil_b200_main.argtypes = [c.c_void_p, c.c_int]
     lib.anvil_b200_step.restype = c.c_int
     lib.anvil_b200_step.argtypes = [c.c_void_p]
+    lib.anvil_b200_step_fed.restype = c.c_int
+    lib.anvil_b200_step_fed.argtypes = [c.c_void_p]
     return lib

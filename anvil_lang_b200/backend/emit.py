@@ -747,6 +747,9 @@ class ProgramGen:
         self.hot = an.hot_loop(prog)
         self.hot_body: list[str] | None = None
         self.hot_counter = None
+        self.hot_body_fed: list[str] | None = None
+        self.feed_bufs: list = []
+        self.feed_kernels: list = []
 
     def fault(self, message: str) -> int:
         if message in self.faults:
@@ -789,7 +792,7 @@ class ProgramGen:
         return idx
 
     # ---- host control flow (anvil/backend/cuda.py:429-473)
-    def block(self, b: kir.Block, ind: str, in_loop: bool, tail: list[str] | None = None) -> list[str]:
+    def block(self, b: kir.Block, ind: str, in_loop: bool, tail: list[str] | None = None, skip=()) -> list[str]:
         """`tail`: host calls to issue right after the block's last statement (the loop counter
         increment); they join the last launch run when the block ends with one."""
         out = []
@@ -801,10 +804,17 @@ class ProgramGen:
             if isinstance(st, kir.KernelStmt):
                 j = i
                 run = []
+                calls = []
                 while j < len(stmts) and isinstance(stmts[j], kir.KernelStmt):
-                    run.append(self.add_kernel(stmts[j].kernel))
+                    kj = stmts[j].kernel
+                    idx = self.add_kernel(kj)
+                    if kj.id in skip:                # fed from the host; its random stream is still consumed
+                        if kj.uses_rand():
+                            calls.append("anvil_rt_set_stream(rt, anvil_rt_get_stream(rt) + 1u);")
+                    else:
+                        run.append(idx)
+                        calls.append(f"RT(launch_{idx}(rt));")
                     j += 1
-                calls = [f"RT(launch_{idx}(rt));" for idx in run]
                 if j == len(stmts) and tail is not None:
                     calls += tail
                     tail_done = True
@@ -896,6 +906,9 @@ class ProgramGen:
             body = self.block(st.body, ind + "        ", True, tail)
             if is_hot:
                 self.hot_body = self.block(st.body, "    ", True, tail)
+                feed_k, self.feed_bufs = an.input_producers(self.prog, st)
+                self.feed_kernels = feed_k
+                self.hot_body_fed = self.block(st.body, "    ", True, tail, skip={k.id for k in feed_k})
                 self.hot_counter = st.counter
                 out.append(f"{ind}    if (mode == 1) return 2;     // paused at the training loop")
             out.append(f"{ind}    for (long {i} = {lo}; {i} < {hi}; {i} += {st.step}) {{")
@@ -1010,6 +1023,11 @@ class ProgramGen:
         out += ['extern "C" int anvil_b200_step(anvil_rt *rt) {   // one iteration of the training loop']
         if self.hot_body is not None:
             out += self.hot_body + ["    return 0;", "}"]
+        else:
+            out += ["    return anvil_rt_set_error(rt, \"anvil: the program has no training loop\");", "}"]
+        out += ['extern "C" int anvil_b200_step_fed(anvil_rt *rt) {   // the same, inputs already copied in by the caller']
+        if self.hot_body_fed is not None:
+            out += self.hot_body_fed + ["    return 0;", "}"]
         else:
             out += ["    return anvil_rt_set_error(rt, \"anvil: the program has no training loop\");", "}"]
         # anvil.function ABI (anvil/pyapi.py:237-299): pointer slots + anvil_entry, host arrays

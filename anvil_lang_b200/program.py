@@ -111,6 +111,17 @@ class DeviceProgram:
     def step(self):
         self._check(self.lib.anvil_b200_step(self.rt))
 
+    def step_fed(self):
+        """One training iteration whose input tensors (`self.gen.feed_bufs`) the caller has already
+        written, e.g. with `copy_in_async` from pinned host memory."""
+        self._check(self.lib.anvil_b200_step_fed(self.rt))
+
+    def copy_in_async(self, b: kir.Buffer, host_ptr: int, nbytes: int):
+        self._check(self.rtlib.anvil_rt_h2d_async(self.rt, self.plan.off(b), host_ptr, nbytes))
+
+    def copy_out_async(self, host_ptr: int, b: kir.Buffer, nbytes: int):
+        self._check(self.rtlib.anvil_rt_d2h_async(self.rt, host_ptr, self.plan.off(b), nbytes))
+
     def launch(self, kernel: kir.Kernel | int):
         idx = kernel if isinstance(kernel, int) else self.gen.kernel_index[kernel.id]
         self._check(self.lib.anvil_b200_launch(self.rt, idx))

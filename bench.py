@@ -1,0 +1,331 @@
+"""Benchmark: train samples/s of a BASELINE configuration on N B200s, one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5|c3|c4|c1] [--impl b200|reference]
+
+A step is one iteration of the program's training loop (forward, backward, optimizer update).
+`value` times K steps on the device with CUDA events on the program's stream, inputs produced on
+the device; `e2e` times the same steps through the host-fed path: inputs prepared in pinned host
+memory, copied in every step, the loss copied back every step. The dominant kernel's roofline and a
+CPU baseline (the oracle's NumPy restatement of the reference interpreter, on a bounded sample) ride
+on the same line. `--impl reference` prints the CPU arm alone.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "c5": ("c5_transformer", 64, "decoder-only char transformer 6L D512 H8 T256 vocab 256, f32, Adam lr 3e-4, global batch 64"),
+    "c3": ("c3_mlp_adam", 256, "MLP 784-1024-1024-10, f32, cross_entropy, Adam lr 1e-3, batch 256"),
+    "c4": ("c4_cnn_sgd", 128, "CNN conv3x3 1-32-64 + linear 1600-10, f32, SGD lr 0.05, batch 128"),
+    "c1": ("c1_mlp_sgd", 64, "MLP 784-128-10, f32, cross_entropy, SGD lr 0.1, batch 64"),
+}
+L2_BYTES = 126 << 20
+
+
+def load_program(name):
+    from anvil_lang_b200 import kir
+    return kir.load(os.path.join(ROOT, "anvil_lang_b200", "programs", f"{name}.kir.json.gz"))
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def measure_tf32_peak():
+    """Dense TF32 matmul throughput measured like the driver measures bf16: torch.matmul 8192^3,
+    best of 10, CUDA events. The 3xTF32 roof is a third of it."""
+    try:
+        import torch
+        torch.backends.cuda.matmul.allow_tf32 = True
+        a = torch.randn(8192, 8192, device="cuda")
+        b = torch.randn(8192, 8192, device="cuda")
+        for _ in range(3):
+            a @ b
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            a @ b
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        del a, b
+        torch.cuda.empty_cache()
+        return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device=0):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={device}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        if not sm:
+            return None
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(name, batch, budget_s=20.0):
+    """The CPU baseline: the oracle (NumPy restatement of the reference interpreter, reduction bodies
+    materialised and summed like anvil/interp.py:435-466) runs the program's start-up and then the
+    training step's kernels in order until `budget_s` seconds of kernel time have passed. Throughput
+    for the whole step is extrapolated by the share of the step's FLOPs that the sample covered."""
+    from anvil_lang_b200 import kir
+    from anvil_lang_b200.backend import analysis as an
+    from oracle.kir_interp import Oracle
+    prog = load_program(name)
+    hot = an.hot_loop(prog)
+    o = Oracle(prog, out=open(os.devnull, "w"), seed=0)
+
+    class Reached(Exception):
+        pass
+
+    def run_until_hot(block):
+        for st in block.stmts:
+            if st is hot:
+                o.arr(hot.counter)[0] = hot.start if isinstance(hot.start, int) else o.bound(hot.start)
+                raise Reached()
+            if isinstance(st, kir.For):
+                o.arr(st.counter)[0] = o.bound(st.start)
+                run_until_hot(st.body)
+            else:
+                o.stmt(st)
+    try:
+        run_until_hot(prog.main)
+    except Reached:
+        pass
+    kernels = [st.kernel for st in hot.body.stmts if isinstance(st, kir.KernelStmt)]
+    total_flops = sum(an.kernel_flops(k) for k in kernels)
+    done_flops, spent, n = 0, 0.0, 0
+    for k in kernels:
+        t = time.perf_counter()
+        o.kernel(k)
+        spent += time.perf_counter() - t
+        done_flops += an.kernel_flops(k)
+        n += 1
+        if spent >= budget_s:
+            break
+    step_seconds = spent * total_flops / max(done_flops, 1)
+    return {"value": batch / step_seconds, "unit": "samples/s", "cores": 1, "kind": "port",
+            "sample": f"first {n} of {len(kernels)} kernels of one full-size training step "
+                      f"({100.0 * done_flops / total_flops:.2f}% of its FLOPs, {spent:.1f} s), extrapolated by FLOP share"}
+
+
+def reference_arm(args, name, batch, desc):
+    """`--impl reference`: the CPU implementation alone. Each step is one bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    vals, last = [], None
+    for i in range(args.warmup + args.steps):
+        last = cpu_sample(name, batch, budget_s=args.cpu_budget)
+        if i >= args.warmup:
+            vals.append(last["value"])
+    v = float(np.median(vals))
+    last["value"] = v
+    line = {"impl": "reference", "metric": "train samples/s", "value": v, "unit": "samples/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * batch / v, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (program RNG, seed 0)",
+            "config": {"workload": desc, "global_batch": batch}, "cpu_baseline": last,
+            "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-budget", type=float, default=20.0)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    name, batch, desc = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return reference_arm(args, name, batch, desc)
+    if args.gpus > 1:
+        from anvil_lang_b200 import dp as dpmod
+        return dpmod.bench_main(args, name, batch, desc)
+
+    from anvil_lang_b200 import kir
+    from anvil_lang_b200.backend import analysis as an
+    from anvil_lang_b200.feed import HostFeeder, Unsupported, pinned_array
+    from anvil_lang_b200.program import DeviceProgram
+
+    prog = load_program(name)
+    dp = DeviceProgram(prog, seed=0, device=0)
+    dp.rtlib.anvil_rt_capture(dp.rt, 1)                 # the program's own prints stay off stdout
+    dp.prologue()
+    loss = dp.buffer("loss")
+    hot = an.hot_loop(prog)
+    kernels = [st.kernel for st in hot.body.stmts if isinstance(st, kir.KernelStmt)]
+    step_bytes = sum(an.kernel_bytes(k) for k in kernels)
+    flush = step_bytes < 2 * L2_BYTES                   # working set may sit in L2: evict it between steps
+    W, K = args.warmup, args.steps
+    for _ in range(W):
+        dp.step()
+    dp.sync()
+    dp.rtlib.anvil_rt_capture(dp.rt, 1)                 # (re)starting capture drops the text so far
+
+    # ---- device-resident steps, CUDA events on the program's stream
+    clocks = ClockSampler()
+    launches0 = dp.launches
+    t_wall = time.perf_counter()
+    if not flush:
+        dp.timer_begin()
+        for _ in range(K):
+            dp.step()
+        ms = dp.timer_end()
+    else:
+        ms = 0.0
+        for _ in range(K):
+            flush_l2(dp)
+            dp.timer_begin()
+            dp.step()
+            ms += dp.timer_end()
+    wall = time.perf_counter() - t_wall
+    launches = dp.launches - launches0
+    last_loss = float(dp.read(loss).reshape(-1)[0])
+    value = batch * K / (ms * 1e-3)
+
+    # ---- end to end: inputs from pinned host memory every step, loss back to the host every step
+    e2e = None
+    try:
+        feeder = HostFeeder(dp)
+        feeder.load_host_copies()
+        host_loss = pinned_array(dp.rtlib, (1,), np.float32)
+        seed = dp.seed
+        counter = int(dp.read(hot.counter).reshape(-1)[0])
+        stream = int(dp.rtlib.anvil_rt_get_stream(dp.rt))
+        for i in range(2):                               # warm the fed path (its own launch graph)
+            feeder.prepare(counter, stream, seed)
+            feeder.push()
+            dp.step_fed()
+            counter += hot.step
+            stream += feeder.rand_streams
+        dp.sync()
+        t0 = time.perf_counter()
+        for i in range(K):
+            feeder.prepare(counter, stream, seed)
+            feeder.push()
+            dp.step_fed()
+            dp.copy_out_async(host_loss.ctypes.data, loss, 4)
+            dp.sync()
+            counter += hot.step
+            stream += feeder.rand_streams
+        t_e2e = time.perf_counter() - t0
+        e2e = {"value": batch * K / t_e2e, "unit": "samples/s", "h2d_bytes_per_step": feeder.bytes_per_step,
+               "d2h_bytes_per_step": 4, "ms_per_step": 1e3 * t_e2e / K, "loss": float(host_loss[0])}
+    except Unsupported as e:
+        e2e = {"value": None, "unit": "samples/s", "why": str(e)}
+    clk = clocks.stop()
+
+    # ---- the dominant kernel and its roofline
+    rows = []
+    for k in kernels:
+        rows.append((dp.time_kernel(k, 3), k))
+    total_k = sum(r[0] for r in rows)
+    top_ms, top = max(rows, key=lambda r: r[0])
+    note = dp.gen.kernel_notes[dp.gen.kernel_index[top.id]]
+    peaks = measured_peaks()
+    if note.startswith("gemm"):
+        tf32 = measure_tf32_peak()
+        flops = an.kernel_flops(top)
+        achieved = flops / (top_ms * 1e-3) / 1e12
+        peak = (tf32 / 3.0) if tf32 else 1590.0 / 2 / 3
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "traffic": None, "kernel": f"{top.name} {top.label} [{note}]", "share_of_step": top_ms / total_k,
+                "peak_source": "torch.matmul tf32 8192^3 best of 10, measured in this run, / 3 for 3xTF32" if tf32
+                else "fallback: half the bf16 fallback peak / 3"}
+    else:
+        nbytes = an.kernel_bytes(top)
+        achieved = nbytes / (top_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": f"{top.name} {top.label} [{note}]",
+                "share_of_step": top_ms / total_k, "peak_source": peaks["source"]}
+    classes = {}
+    for t, k in rows:
+        c = dp.gen.kernel_notes[dp.gen.kernel_index[k.id]].split()[0]
+        classes[c] = classes.get(c, 0.0) + t
+    roof["step_ms_by_class"] = {c: round(v, 3) for c, v in sorted(classes.items(), key=lambda kv: -kv[1])}
+
+    cpu = None if args.no_cpu else cpu_sample(name, batch, budget_s=args.cpu_budget)
+    line = {"metric": "train samples/s", "value": value, "unit": "samples/s", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic (the program's own seeded RNG, seed 0)",
+            "config": {"workload": desc, "global_batch": batch, "parallelism": "dp1",
+                       "l2": ("per-step traffic %.0f MB exceeds the 126 MB L2, no flush" % (step_bytes / 1e6)) if not flush
+                       else "L2 flushed with a 256 MB write between timed steps"},
+            "e2e": e2e, "gpu_launches": int(launches), "clocks": clk, "roofline": roof, "cpu_baseline": cpu,
+            "wall_ms_per_step": 1e3 * wall / K, "last_loss": last_loss}
+    print(json.dumps(line))
+    dp.close()
+    return 0
+
+
+_flush_buf = {}
+
+
+def flush_l2(dp):
+    """Evicts L2 by writing 256 MB of device memory with torch (outside the timed events)."""
+    import torch
+    if "t" not in _flush_buf:
+        _flush_buf["t"] = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush_buf["t"].zero_()
+    torch.cuda.synchronize()
+
+
+if __name__ == "__main__":
+    sys.exit(main())
