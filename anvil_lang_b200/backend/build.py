@@ -50,8 +50,7 @@ def _stamp(paths) -> str:
 
 
 def runtime_sources():
-    return [os.path.join(CSRC, "anvil_rt.cu"), os.path.join(CSRC, "anvil_gemm.cu"), os.path.join(CSRC, "anvil_rng.h"),
-            os.path.join(CSRC, "anvil_gemm_sm100.cuh"), os.path.join(INCLUDE, "anvil_cuda.h")]
+    return [os.path.join(CSRC, "anvil_rt.cu"), os.path.join(CSRC, "anvil_rng.h"), os.path.join(INCLUDE, "anvil_cuda.h")]
 
 
 def build_runtime(force: bool = False) -> str:
@@ -81,7 +80,7 @@ def build_program(source: str, path: str | None = None) -> str:
     """Compile generated source to a shared library; cached by content hash under the build dir."""
     os.makedirs(BUILD_DIR, exist_ok=True)
     deps = _stamp([os.path.join(CSRC, "anvil_device.cuh"), os.path.join(CSRC, "anvil_rng.h"),
-                   os.path.join(CSRC, "anvil_gemm_simt.cuh"),
+                   os.path.join(CSRC, "anvil_gemm_simt.cuh"), os.path.join(CSRC, "anvil_gemm_sm100.cuh"),
                    os.path.join(INCLUDE, "anvil_cuda.h")])
     key = hashlib.sha256((source + deps).encode()).hexdigest()[:16]
     lib = path or os.path.join(BUILD_DIR, f"prog-{key}.so")

@@ -699,6 +699,8 @@ class KernelGen:
             S = max(1, min(296 // (tiles * NB), K // 128, 32))
         AK, BNC = ("true" if c.a_kcontig else "false"), ("true" if c.b_ncontig else "false")
         fn = f"G{k.id}"
+        if use_tensor_cores() and K % 4 == 0 and c.kvars[-1].extent % 4 == 0 and M >= 96 and N >= 64 and K >= 64:
+            return self.gen_gemm_tc(base, c, fn, fa, fb, fe, S)
         src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (CUDA-core tiles, split {S})"),
                f"struct {fn} {{", "    char *__restrict__ A;",
                f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = {NB};",
@@ -721,6 +723,73 @@ class KernelGen:
         self.notes = f"gemm simt {NB}x{M}x{N}x{K} S{S}"
         self.contraction = c
         return "\n".join(src), launch
+
+
+    def functor4(self, sig: str, c, operand, pre: list, kvars) -> list[str]:
+        """`a4` / `b4`: four consecutive k of one operand row, 128-bit loads where the operand is
+        contiguous and aligned along k."""
+        saved = self.ptrs
+        self.ptrs = {}
+        vv = kvars[-1]
+        ind = "        "
+        dk = self.decode("((uint32_t)k >> 2)", kvars, self.names, ind, vv, 4) + self.lane_vars(vv, 4, ind)
+        sc = Scope(self, self.names, 4, vv, ind)
+        vals = [sc.ex(operand, lane) for lane in range(4)]
+        decls = ["    " + ln for ln in self.pointer_decls()]
+        out = [f"    __device__ __forceinline__ {sig} const {{"] + decls + pre + dk + sc.lines
+        out += [f"{ind}v[{i}] = {x};" for i, x in enumerate(vals)] + ["    }"]
+        self.ptrs = {**saved, **self.ptrs}
+        return out
+
+    def gen_gemm_tc(self, base, c, fn, fa, fb, fe, S):
+        k = self.k
+        M, N, K, NB = c.M, c.N, c.K, c.NB
+        ind = "        "
+        dm = self.decode("(uint32_t)m", c.mvars, self.names, ind)
+        dn = self.decode("(uint32_t)n", c.nvars, self.names, ind)
+        db = self.decode("(uint32_t)bt", c.bvars, self.names, ind) if c.bvars else []
+        fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
+        fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
+        BN = 128 if N >= 128 else 64
+        tiles = ((M + 127) // 128) * ((N + BN - 1) // BN)
+        S = 1
+        if tiles * NB < 148 and K >= 256:
+            S = max(1, min(148 // (tiles * NB), K // 128, 32))
+        AK = "true" if c.a_kcontig else "false"
+        BKC = "true" if ct._contig(c.b, c.kvars[-1]) else "false"
+        src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (tcgen05 3xTF32, 128x{BN} tiles, split {S})"),
+               f"struct {fn} {{", "    char *__restrict__ A;",
+               f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = {NB};",
+               f"    static constexpr float ALPHA = {flit(c.alpha)};"] + fa4 + fb4 + fe + ["};"]
+        smem = f"anvil::tc::smem_bytes({BN})"
+        status = "(uint32_t *)(A + ANVIL_RT_STATUS_OFF)"
+        launch = []
+        if S == 1:
+            kname = base
+            src += [f"__global__ void __launch_bounds__(288, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                    f"    anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, 1>({fn}{{A}}, nullptr, {status});", "}"]
+        else:
+            kname = base + "_part"
+            self.gen.need_scratch(4 * M * N * NB * S)
+            soff = self.gen.plan.scratch_off
+            src += [f"__global__ void __launch_bounds__(288, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                    f"    anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, {S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
+                    f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                    f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
+        launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
+                      f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
+        launch.append(f"{kname}<<<dim3({tiles}, {NB * S}), 288, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        if S > 1:
+            fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
+            launch.append(self.launch_line(base, fb_, 256))
+        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}"
+        self.contraction = c
+        return "\n".join(src), launch
+
+
+def use_tensor_cores() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_TC", "1") != "0"
 
 
 def index_t(n: int) -> str:
@@ -997,7 +1066,7 @@ class ProgramGen:
         externs = [b for b in self.prog.roots() if b.kind in ("input", "output")]
         out = [f"// Generated by anvil-b200 from {self.prog.name}: sm_100a kernels over one device arena.",
                "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
-               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', "",
+               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', '#include "anvil_gemm_sm100.cuh"', "",
                "#define RT(call) do { if ((call) != 0) return 1; } while (0)", ""]
         out += self.tables + [""]
         out.append("static const char *const fault_messages[] = {\"\", " + ", ".join(c_string(m) for m in self.faults)

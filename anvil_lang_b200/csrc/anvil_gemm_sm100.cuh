@@ -1,0 +1,262 @@
+// anvil_gemm_sm100.cuh — tensor-core contraction template for sm_100a: tcgen05.mma (kind::tf32) with the
+// accumulator in tensor memory, f32 accuracy recovered by the 3xTF32 split.
+//
+//   C[b, m, n] = epilogue(alpha * sum_k A[b, m, k] * B[b, k, n])        (same functor contract as
+//                                                                        anvil_gemm_simt.cuh)
+//
+// One CTA computes a 128 x BN tile. Nine warps:
+//   warps 0-7  "converters": read operand values through the generated functor (so prologues such as
+//              max(x, 0), scales and gathers cost nothing extra), split every f32 x into
+//              hi = x with the low 13 mantissa bits cleared (exactly a TF32 value) and lo = x - hi
+//              (exact in f32), and write both into shared memory in the tensor core's canonical
+//              K-major no-swizzle layout: 16-byte chunk (row r, k-chunk c) at  c * LBO + r * 16.
+//   warp 8     one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs (hi*lo, lo*hi, hi*hi) into
+//              the same TMEM accumulator and commits the stage's "empty" barrier.
+//   warps 0-7  afterwards read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp), transpose
+//              32 x 32 blocks through shared memory so that consecutive lanes hold consecutive n, and
+//              run the kernel's statements (the epilogue functor) with coalesced stores.
+// A 3-stage ring of {A hi, A lo, B hi, B lo} tiles (64.5 KB per stage at BN = 128) is handed back
+// and forth with mbarriers: converters arrive on full[s] after a generic->async proxy fence, the MMA
+// thread's tcgen05.commit arrives on empty[s].
+//
+// Every wait is bounded by a clock: a barrier that does not flip within about a second makes the
+// waiting thread record ANVIL_TC_TIMEOUT in the arena header's status word and leave its loop; the
+// CTA still meets at the final barrier and frees its tensor memory. Nothing here traps.
+//
+// Accumulation order is fixed by the tile shape alone: results are bit-reproducible.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace anvil {
+namespace tc {
+
+constexpr int BM = 128, BK = 32, STAGES = 3;
+constexpr int CONV_THREADS = 256, THREADS = 288;
+constexpr uint32_t TIMEOUT = 0x7C05u;
+
+__host__ __device__ constexpr uint32_t lbo_bytes(int rows) { return (uint32_t)rows * 16u + 16u; }   // +16: no bank aliasing between k-chunks
+__host__ __device__ constexpr uint32_t tile_bytes(int rows) { return (BK / 4) * lbo_bytes(rows); }
+__host__ __device__ constexpr uint32_t stage_bytes(int bn) { return 2 * tile_bytes(BM) + 2 * tile_bytes(bn); }
+__host__ __device__ constexpr uint32_t smem_bytes(int bn) { return STAGES * stage_bytes(bn) + 256; }
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: false if the phase did not complete within ~2^31 clocks.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (true) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > (1LL << 31)) return false;
+    }
+}
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo) {
+    // K-major, no swizzle: start >> 4 | LBO >> 4 at bit 16 | SBO >> 4 at bit 32 | version 1 at bit 46
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
+}
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    // D = f32 (1 << 4), A and B = TF32 (2 << 7, 2 << 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// One operand tile of a k block, as the converter threads see it. ROWS x 32 values = ROWS/32 chunks
+// of 4 per thread. KC (the operand is contiguous along k in memory): 8 consecutive lanes take the 8
+// chunks of one row, so a warp reads 4 full 128-byte row segments. Otherwise consecutive lanes take
+// consecutive rows. Either way a quarter warp's 16-byte shared stores fall into distinct banks.
+template <bool KC, int ROWS>
+struct TileMap {
+    static constexpr int P = ROWS / 32;
+    __device__ __forceinline__ static void at(int t, int p, int &row, int &kc) {
+        if (KC) { kc = t % 8; row = t / 8 + 32 * p; }
+        else { row = t % ROWS; kc = t / ROWS + (CONV_THREADS / ROWS) * p; }
+    }
+};
+
+__device__ __forceinline__ void split_store(uint8_t *hi_tile, uint8_t *lo_tile, uint32_t off, const float (&v)[4]) {
+    float4 hi, lo;
+    hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
+    hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xFFFFE000u); lo.y = v[1] - hi.y;
+    hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xFFFFE000u); lo.z = v[2] - hi.z;
+    hi.w = __uint_as_float(__float_as_uint(v[3]) & 0xFFFFE000u); lo.w = v[3] - hi.w;
+    *reinterpret_cast<float4 *>(hi_tile + off) = hi;
+    *reinterpret_cast<float4 *>(lo_tile + off) = lo;
+}
+
+// F: M, N, K, NB, ALPHA; a4(m, k, b, v[4]) / b4(k, n, b, v[4]) give 4 consecutive k; epi(m, n, b, acc).
+// AK / BKC: operand is contiguous along k. SPLIT > 1: blockIdx.y % SPLIT picks a k range and the raw
+// tile goes to `partial`. Requires F::K % 4 == 0.
+template <class F, bool AK, bool BKC, int BN, int SPLIT>
+__device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ partial, uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int M = F::M, N = F::N, K = F::K;
+    constexpr int TILES_N = (N + BN - 1) / BN;
+    constexpr uint32_t LBO_A = lbo_bytes(BM), LBO_B = lbo_bytes(BN);
+    constexpr uint32_t TA = tile_bytes(BM), TB = tile_bytes(BN), STAGE = stage_bytes(BN);
+    constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK - 1) / BK * BK;          // k range of one split
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int tile_m = blockIdx.x / TILES_N, tile_n = blockIdx.x % TILES_N;
+    const int bt = SPLIT > 1 ? blockIdx.y / SPLIT : blockIdx.y;
+    const int sp = SPLIT > 1 ? blockIdx.y % SPLIT : 0;
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
+    const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
+    const int nkb = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE);         // full[3], empty[3], accum
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE + 64);
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + STAGES * STAGE + 72);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    const uint32_t accum = bar0 + 8u * (2 * STAGES);
+
+    if (t == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full(s), CONV_THREADS); mbar_init(empty(s), 1); }
+        mbar_init(accum, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        // ---------------------------------------------------------------- converters
+        float va[BM / 32][4], vb[BN / 32][4];
+        auto fetch = [&](int k0) {
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(t, p, row, kc);
+                const int m = m0 + row, k = k0 + kc * 4;
+                if (m < M && k < k_end) f.a4(m, k, bt, va[p]);
+                else { va[p][0] = va[p][1] = va[p][2] = va[p][3] = 0.0f; }
+            }
+#pragma unroll
+            for (int p = 0; p < BN / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BN>::at(t, p, row, kc);
+                const int n = n0 + row, k = k0 + kc * 4;
+                if (n < N && k < k_end) f.b4(k, n, bt, vb[p]);
+                else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+            }
+        };
+        if (nkb > 0) fetch(k_begin);
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
+            uint8_t *st = smem + s * STAGE;
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(t, p, row, kc);
+                split_store(st, st + TA, kc * LBO_A + row * 16, va[p]);
+            }
+#pragma unroll
+            for (int p = 0; p < BN / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BN>::at(t, p, row, kc);
+                split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
+            }
+            if (kb + 1 < nkb) fetch(k_begin + (kb + 1) * BK);      // next block's loads fly during the wait below
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(full(s));
+        }
+    } else if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr uint32_t IDESC = instr_desc(BM, BN);
+        const uint32_t base = smem_u32(smem);
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(full(s), ph)) { *failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
+#pragma unroll
+            for (int j = 0; j < BK / 8; j++) {
+                const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_A, LBO_A), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
+                const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
+                mma_tf32(tmem, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
+                mma_tf32(tmem, dal, dbh, IDESC, 1u);
+                mma_tf32(tmem, dah, dbh, IDESC, 1u);
+            }
+            mma_commit(empty(s));
+        }
+        mma_commit(accum);
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    if (warp < 8) {
+        const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
+        if (!ok) *failed = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);    // this warp's 32 x 32 transpose block
+        const int q = warp & 3;                                                  // TMEM lanes 32q .. 32q + 31
+        constexpr int CHUNKS = BN / 32;
+        for (int c = warp >> 2; c < CHUNKS; c += 2) {
+            uint32_t r[32];
+            if (ok && nkb > 0) tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
+            else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]);
+            __syncwarp();
+            const int n = n0 + 32 * c + lane;
+            for (int rr = 0; rr < 32; rr++) {
+                const int m = m0 + 32 * q + rr;
+                const float v = stage_f[rr * 33 + lane];
+                if (m < M && n < N) {
+                    if (SPLIT > 1) partial[(((long)bt * SPLIT + sp) * M + m) * N + n] = v;
+                    else f.epi(m, n, bt, v * F::ALPHA);
+                }
+            }
+            __syncwarp();
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+    }
+    if (t == 0 && *failed) atomicExch(status, TIMEOUT);
+}
+
+}  // namespace tc
+}  // namespace anvil

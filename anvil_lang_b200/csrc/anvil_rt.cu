@@ -493,6 +493,12 @@ extern "C" int anvil_rt_fault_messages(anvil_rt *rt, const char *const *messages
 extern "C" int anvil_rt_check_faults(anvil_rt *rt) {
     struct { int code; int pad; long long value; } f;
     if (anvil_rt_d2h(rt, &f, ANVIL_RT_FAULT_OFF, sizeof f)) return 1;
+    uint32_t status = 0;
+    if (anvil_rt_d2h(rt, &status, ANVIL_RT_STATUS_OFF, 4)) return 1;
+    if (status) {
+        fflush(stdout);
+        return fail(rt, "anvil: runtime error: a kernel gave up waiting on a barrier (status 0x%x)", status);
+    }
     if (!f.code) return 0;
     const char *m = (f.code > 0 && f.code < rt->n_fault_messages && rt->fault_messages[f.code])
                         ? rt->fault_messages[f.code] : "index out of bounds";

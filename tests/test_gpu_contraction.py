@@ -1,0 +1,69 @@
+"""The contraction templates against float64 matmul, through generated code and the C ABI.
+
+Covers both templates (tcgen05 3xTF32 tiles and the CUDA-core tiles), operand transposes, batch,
+ragged M / N / K tails, split-k, operand prologue, bias / relu / alpha / += epilogues. Tolerance:
+1e-5 of the output's magnitude (the project bar is 1e-4; 3xTF32 and f32 FMA both sit near 1e-6)."""
+import os
+
+import numpy as np
+import pytest
+
+from anvil_lang_b200.program import DeviceProgram
+from kirbuild import contraction_program, contraction_reference
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out
+    (128, 128, 64, 1, False, False, False, False, 1.0, False, False),
+    (256, 256, 256, 1, False, False, True, False, 1.0, False, True),
+    (384, 192, 512, 1, False, True, False, True, 1.0, False, False),
+    (200, 136, 100, 1, True, False, False, False, 0.125, False, False),      # ragged tails, K % 32 != 0
+    (512, 512, 4096, 1, True, False, False, False, 1.0, True, False),        # split-k, += into C
+    (256, 64, 256, 6, False, False, False, False, 0.125, False, False),      # batched, 64-wide tile
+    (256, 256, 64, 4, False, True, False, False, 1.0, False, False),
+    (130, 70, 36, 2, True, True, True, False, 1.0, False, False),
+    (1024, 1024, 1024, 1, False, False, True, False, 1.0, False, False),
+]
+
+
+def run_case(case, tc):
+    M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out = case
+    os.environ["ANVIL_B200_TC"] = "1" if tc else "0"
+    try:
+        prog, kern, A, B, C, bias_b = contraction_program(M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out)
+        dp = DeviceProgram(prog, graphs=False)
+    finally:
+        os.environ.pop("ANVIL_B200_TC", None)
+    note = dp.gen.kernel_notes[0]
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal(A.numel, dtype=np.float32)
+    b = rng.standard_normal(B.numel, dtype=np.float32)
+    c0 = rng.standard_normal(C.numel, dtype=np.float32)
+    bv = rng.standard_normal(N, dtype=np.float32)
+    dp.write(A, a); dp.write(B, b); dp.write(C, c0); dp.write(bias_b, bv)
+    dp.launch(kern)
+    dp.check_faults()
+    got = dp.read(C).astype(np.float64)
+    dp.close()
+    want = contraction_reference(a, b, c0, bv, M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out)
+    err = np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+    return err, note
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[:4])))
+def test_tensor_core_contraction(case):
+    err, note = run_case(case, tc=True)
+    assert err < 1e-5, (err, note)
+
+
+@pytest.mark.parametrize("case", CASES[:8], ids=lambda c: "x".join(map(str, c[:4])))
+def test_cuda_core_contraction(case):
+    err, note = run_case(case, tc=False)
+    assert "simt" in note or "coop" in note or "thread" in note
+    assert err < 1e-5, (err, note)
+
+
+def test_large_shapes_take_the_tensor_core_template():
+    _, note = run_case(CASES[1], tc=True)
+    assert note.startswith("gemm tc")
