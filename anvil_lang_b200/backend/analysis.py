@@ -142,10 +142,21 @@ def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256) -> 
     scratch_off = pos
     pos += up(max(scratch_bytes, 4))
     offsets = {}
+    bucket = [b.root for b in getattr(prog, "bucket", [])]
+    bucket_off = pos
+    for r in bucket:                                 # the all-reduce bucket is one contiguous span
+        if r.id not in offsets:
+            offsets[r.id] = pos
+            pos += up(max(r.nbytes, 16))
+    bucket_bytes = pos - bucket_off
     for r in prog.roots():
+        if r.id in offsets:
+            continue
         offsets[r.id] = pos
         pos += up(max(r.nbytes, 16))
-    return ArenaPlan(offsets, pos, scratch_off, up(max(scratch_bytes, 4)))
+    plan = ArenaPlan(offsets, pos, scratch_off, up(max(scratch_bytes, 4)))
+    plan.bucket_off, plan.bucket_bytes = bucket_off, bucket_bytes
+    return plan
 
 
 # ----------------------------------------------------------------------------- algorithmic work

@@ -132,6 +132,7 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_graphs": (None, [P, I]), "anvil_rt_launch_count": (L, [P]),
         "anvil_rt_timer_begin": (I, [P]), "anvil_rt_timer_end": (I, [P, c.POINTER(c.c_float)]),
         "anvil_rt_time_launch": (I, [P, P, I, I, c.POINTER(c.c_float)]),
+        "anvil_rt_set_allreduce": (None, [P, P, P]), "anvil_rt_allreduce": (I, [P, Z, L]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

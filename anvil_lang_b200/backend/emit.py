@@ -345,6 +345,8 @@ class KernelGen:
     def rand_index(self, scope: Scope, lane) -> str:
         strides = kir.row_major_strides([v.extent for v in self.k.domain])
         parts = [f"{s}u * (uint32_t){scope.var(v, lane)}" for v, s in zip(self.k.domain, strides)]
+        if self.k.rand_base:
+            parts.append(f"{self.k.rand_base & 0xFFFFFFFF}u")
         return " + ".join(parts) if parts else "0u"
 
     def pointer_decls(self) -> list[str]:
@@ -926,6 +928,8 @@ class ProgramGen:
             if st.orelse.stmts:
                 out += [f"{ind}}} else {{"] + self.block(st.orelse, ind + "    ", in_loop)
             return out + [f"{ind}}}", f"{ind}}}"]
+        if isinstance(st, kir.AllReduce):
+            return [f"{ind}RT(anvil_rt_allreduce(rt, {self.plan.bucket_off}UL, {self.plan.bucket_bytes // 4}L));"]
         if isinstance(st, kir.Break):
             return [f"{ind}break;"]
         if isinstance(st, kir.Continue):

@@ -46,6 +46,8 @@ struct anvil_rt {
     std::map<int, anvil_graph> graphs;
     long launches = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    anvil_allreduce_fn allreduce = nullptr;
+    void *allreduce_user = nullptr;
 };
 
 static double now_seconds() {
@@ -593,5 +595,19 @@ extern "C" int anvil_rt_time_launch(anvil_rt *rt, anvil_launch_fn launch, int in
     float total = 0;
     CK(rt, cudaEventElapsedTime(&total, rt->ev0, rt->ev1));
     *ms = total / repeats;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------- collective
+extern "C" void anvil_rt_set_allreduce(anvil_rt *rt, anvil_allreduce_fn fn, void *user) {
+    rt->allreduce = fn;
+    rt->allreduce_user = user;
+}
+extern "C" int anvil_rt_allreduce(anvil_rt *rt, size_t off, long count) {
+    if (in_range(rt, off, 4 * (size_t)count)) return 1;
+    if (!rt->allreduce) return fail(rt, "anvil: the program was sharded over several GPUs but no collective is attached");
+    if (rt->capturing_key >= 0) return fail(rt, "anvil: a collective inside a recorded launch sequence");
+    if (rt->allreduce(rt->allreduce_user, rt->arena + off, count, (void *)rt->stream))
+        return fail(rt, "anvil: the all-reduce failed");
     return 0;
 }

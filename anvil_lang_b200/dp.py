@@ -1,0 +1,189 @@
+"""Data-parallel training over the GPUs of one node: batch sharding with ONE all-reduce per step.
+
+The reference has no multi-device code. The scheme here keeps the *global* computation identical to
+the single-GPU program: rank r of G runs the program compiled for the local batch b = B / G, and
+`shard()` rewrites it so that
+
+  1. batch gathers read rows  perm[B * step + r * b + i]  (the rank's slice of the global batch) and
+     the batch loop runs N / B times;
+  2. kernels that sample a step's inputs draw element r * b * rowlen + i of the global tensor
+     (`Kernel.rand_base`), so the ranks' samples are slices of the single-GPU draw;
+  3. every kernel that updates parameters or optimizer state is split at its reduction: the gradient
+     goes to a buffer in a contiguous "bucket", the update becomes an elementwise kernel that reads
+     1/G times the bucket; all updates move behind a single `kir.AllReduce` of the bucket (the loss
+     rides along), so parameters stay bit-identical on every rank.
+
+Parameter initialisation and the shuffle are untouched: same seed, same bits on every rank.
+The collective itself is NCCL through `torch.distributed` on the program's stream (`attach`).
+"""
+from __future__ import annotations
+
+import itertools
+
+from . import kir
+from .backend import analysis as an
+from .kir import F32, Affine, E, Kernel, KernelStmt, Let, Store
+
+UPDATED_KINDS = ("param", "state")
+
+
+class ShardError(Exception):
+    pass
+
+
+def _rewrite(e: E, fn, memo: dict, lets: dict) -> E:
+    """Rebuilds an expression bottom-up; `fn(node)` may return a replacement for leaves."""
+    hit = memo.get(id(e))
+    if hit is not None:
+        return hit
+    r = fn(e)
+    if r is None:
+        if e.k == "let":
+            r = E("let", e.dt, let=lets[e.let.id])
+        elif e.a:
+            r = E(e.k, e.dt, op=e.op, a=[_rewrite(x, fn, memo, lets) for x in e.a])
+        else:
+            r = e
+    memo[id(e)] = r
+    return r
+
+
+def _identity(domain) -> Affine:
+    strides = kir.row_major_strides([v.extent for v in domain])
+    return Affine(0, list(zip(domain, strides)))
+
+
+def shard(prog: kir.Program, rank: int, world: int) -> kir.Program:
+    """Rewrites `prog` (compiled for the local batch) in place for rank `rank` of `world`."""
+    if world == 1:
+        return prog
+    hot = an.hot_loop(prog)
+    if hot is None:
+        raise ShardError("the program has no training loop")
+    ids = itertools.count(max([b.id for b in prog.buffers] + [k.id for k in prog.kernels()]) + 1000)
+    inv = 1.0 / world
+
+    # ---- 1, 2: the step's inputs
+    producers, _ = an.input_producers(prog, hot)
+    gathers_fixed = False
+    for k in producers:
+        b_local = k.domain[0].extent
+        if k.uses_rand():
+            k.rand_base = rank * b_local * kir.prod(v.extent for v in k.domain[1:])
+            continue
+        for e in [n for x in k.exprs() for n in x.walk() if n.k == "load"]:
+            for g, _ in e.off.gathers():
+                srefs = g.offset.scalars()
+                if len(srefs) == 1 and srefs[0][0].buf.root is hot.counter.root:
+                    terms = [(t, c * world if isinstance(t, kir.SRef) else c) for t, c in g.offset.terms]
+                    g.offset = Affine(g.offset.const + rank * b_local, terms)
+                    e._key = None
+                    gathers_fixed = True
+    if gathers_fixed:
+        if not (isinstance(hot.start, int) and isinstance(hot.stop, int)):
+            raise ShardError("the batch loop has run-time bounds")
+        hot.stop = hot.start + (hot.stop - hot.start) // world
+
+    # ---- 3: split updates from gradients, move them behind one all-reduce
+    body = hot.body.stmts
+    if not all(isinstance(s, (KernelStmt, kir.Print)) for s in body):
+        raise ShardError("the training loop has control flow inside it")
+    kernels = [s.kernel for s in body if isinstance(s, KernelStmt)]
+    prints = [s for s in body if isinstance(s, kir.Print)]
+    is_update = {k.id: any(s.buf.root.kind in UPDATED_KINDS for s in k.stores) for k in kernels}
+    grads: list[kir.Buffer] = []
+    first, updates = [], []
+    for k in kernels:
+        if not is_update[k.id]:
+            first.append(k)
+            continue
+        if k.red is None:
+            updates.append(k)
+            continue
+        g = kir.Buffer(next(ids), f"g.{k.name}", tuple(v.extent for v in k.domain), k.red.dtype, "grad")
+        if g.dtype != F32:
+            raise ShardError(f"{k.name}: an integer reduction feeds an update")
+        prog.buffers.append(g)
+        grads.append(g)
+        ident = _identity(k.domain)
+        first.append(Kernel(next(ids), k.name + "_g", k.label, k.domain, [Store(g, ident, E("acc", F32))], k.red))
+        lets, memo, stmts = {}, {}, []
+
+        def fn(n, g=g, ident=ident):
+            if n.k == "acc":
+                return E("bin", F32, op="mul", a=[E("const", F32, val=inv), E("load", F32, buf=g, off=ident)])
+            return None
+        for st in k.stmts:
+            if isinstance(st, Let):
+                nl = Let(next(ids), st.name, _rewrite(st.value, fn, memo, lets))
+                lets[st.id] = nl
+                stmts.append(nl)
+            else:
+                stmts.append(Store(st.buf, st.offset, _rewrite(st.value, fn, memo, lets), st.accumulate))
+        updates.append(Kernel(next(ids), k.name + "_u", k.label, k.domain, stmts, None))
+
+    # gradients that reach an update kernel through memory (written by non-update kernels)
+    written_first = set()
+    for k in first:
+        written_first |= {b.id for b in k.writes()}
+    grad_ids = {g.id for g in grads}
+    exchanged: dict[int, kir.Buffer] = {}
+    for k in updates:
+        for r in k.reads():
+            if r.id in written_first and r.id not in grad_ids and r.kind not in UPDATED_KINDS and r.numel > 0 \
+                    and r.root is not hot.counter.root:
+                if r.dtype != F32:
+                    raise ShardError(f"{k.name} reads the integer tensor {r.name} computed by the step")
+                exchanged[r.id] = r
+    for i, k in enumerate(updates):
+        if not any(r.id in exchanged for r in k.reads()):
+            continue
+        lets, memo, stmts = {}, {}, []
+
+        def fn2(n):
+            if n.k == "load" and n.buf.root.id in exchanged:
+                return E("bin", F32, op="mul", a=[E("const", F32, val=inv), n])
+            return None
+        for st in k.stmts:
+            if isinstance(st, Let):
+                nl = Let(next(ids), st.name, _rewrite(st.value, fn2, memo, lets))
+                lets[st.id] = nl
+                stmts.append(nl)
+            else:
+                stmts.append(Store(st.buf, st.offset, _rewrite(st.value, fn2, memo, lets), st.accumulate))
+        updates[i] = Kernel(k.id, k.name, k.label, k.domain, stmts, None, k.rand_base)
+
+    # moving the updates to the end must not change what anything reads
+    upd_writes = set()
+    for k in updates:
+        upd_writes |= {b.id for b in k.writes()}
+    pos = {k.id: i for i, k in enumerate(kernels)}
+    orig_of = {}
+    for k in kernels:
+        orig_of[k.name] = k
+    for u in updates:
+        base = orig_of.get(u.name.removesuffix("_u"), None)
+        upos = pos.get(base.id if base is not None else u.id, 0)
+        uw = {b.id for b in u.writes()}
+        ur = {b.id for b in u.reads()}
+        for k in kernels[upos + 1:]:
+            if is_update[k.id]:
+                continue
+            if uw & {b.id for b in k.reads()} or uw & {b.id for b in k.writes()} \
+                    or (ur - set(exchanged) - grad_ids) & {b.id for b in k.writes()}:
+                raise ShardError(f"{k.name} depends on the update {u.name} that would move behind it")
+
+    bucket = grads + list(exchanged.values())
+    tail = []
+    loss = [b for b in prog.buffers if b.name == "loss" and b.root.id in written_first]
+    if loss:
+        lb = loss[-1].root
+        bucket.append(lb)
+        zero = Affine(0)
+        tail.append(Kernel(next(ids), "loss_mean", "mean over ranks", [],
+                           [Store(lb, zero, E("bin", F32, op="mul", a=[E("const", F32, val=inv),
+                                                                        E("load", F32, buf=lb, off=zero)]))], None))
+    prog.bucket = bucket
+    hot.body.stmts = ([KernelStmt(k) for k in first] + [kir.AllReduce(bucket)]
+                      + [KernelStmt(k) for k in tail + updates] + prints)
+    return prog

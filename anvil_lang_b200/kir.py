@@ -269,6 +269,7 @@ class Kernel:
     domain: list
     stmts: list
     red: Reduction | None = None
+    rand_base: int = 0     # added to the element index of every random draw (a rank's slice of a global tensor)
 
     @property
     def stores(self):
@@ -416,10 +417,19 @@ class RTCall:
 
 
 @dataclass(eq=False)
+class AllReduce:
+    """Sum the listed tensors over all ranks (data-parallel training; no reference counterpart: the
+    reference has no multi-device code). The back end lays the tensors out contiguously and issues ONE
+    collective over the span."""
+    bufs: list
+
+
+@dataclass(eq=False)
 class Program:
     main: Block
     buffers: list
     name: str = "<program>"
+    bucket: list = field(default_factory=list)     # tensors an AllReduce sums: laid out contiguously
 
     def kernels(self) -> list[Kernel]:
         out = []

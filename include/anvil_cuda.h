@@ -131,6 +131,13 @@ int anvil_rt_timer_end(anvil_rt *rt, float *milliseconds);    /* synchronises on
 typedef int (*anvil_launch_fn)(anvil_rt *, int);
 int anvil_rt_time_launch(anvil_rt *rt, anvil_launch_fn launch, int index, int repeats, float *milliseconds);
 
+/* ---- the data-parallel collective (no reference counterpart: the reference is single-device).
+ * Sums `count` f32 values at arena offset `off` over all ranks, in place, stream-ordered. The
+ * collective itself is supplied by the host program (NCCL through torch.distributed in this repo). */
+typedef int (*anvil_allreduce_fn)(void *user, void *device_ptr, long count, void *cuda_stream);
+void anvil_rt_set_allreduce(anvil_rt *rt, anvil_allreduce_fn fn, void *user);
+int anvil_rt_allreduce(anvil_rt *rt, size_t off, long count);
+
 #ifdef __cplusplus
 }
 #endif

@@ -154,6 +154,7 @@ class Oracle:
         self.t0 = time.perf_counter()
         self.kernel_count = 0
         self.on_kernel = None                        # hook(kernel) called after each kernel
+        self.allreduce = None                        # hook(list of arrays): sum over ranks, in place
 
     def arr(self, b: kir.Buffer) -> np.ndarray:
         return self.mem[b.root.id]
@@ -206,6 +207,10 @@ class Oracle:
                     continue
         elif isinstance(st, kir.If):
             self.block(st.then if self.arr(st.cond)[0] != 0 else st.orelse)
+        elif isinstance(st, kir.AllReduce):
+            if self.allreduce is None:
+                raise OracleRuntimeError("the program has an all-reduce but no collective was given")
+            self.allreduce([self.arr(b) for b in st.bufs])
         elif isinstance(st, kir.Break):
             raise _Break()
         elif isinstance(st, kir.Continue):
@@ -389,11 +394,11 @@ class Oracle:
             if chunk_red and R:
                 acc = self.reduce_chunked(k, D, R, stream)
             else:
-                ctx = {"env": env, "ndim": len(allv), "stream": stream, "D": D, "lets": {}, "memo": {}}
+                ctx = {"env": env, "ndim": len(allv), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "memo": {}}
                 body = np.broadcast_to(self.eval(k.red.body, ctx), fullshape)
                 acc = self.reduce(k.red.op, body, len(D))
         denv = {v: env[v].reshape(env[v].shape[:len(D)]) for v in D}
-        sctx = {"env": denv, "ndim": len(D), "stream": stream, "D": D, "lets": {}, "acc": acc, "memo": {}}
+        sctx = {"env": denv, "ndim": len(D), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "acc": acc, "memo": {}}
         for st in k.stmts:
             if isinstance(st, kir.Let):
                 sctx["lets"][st.id] = self.eval(st.value, sctx)
@@ -435,7 +440,7 @@ class Oracle:
             e = min(r0.extent, s + per)
             env2 = self.grid(D + R, {r0: (s, e)})
             shape2 = tuple(v.extent for v in D) + tuple((e - s) if v is r0 else v.extent for v in R)
-            ctx = {"env": env2, "ndim": len(D + R), "stream": stream, "D": D, "lets": {}, "memo": {}}
+            ctx = {"env": env2, "ndim": len(D + R), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "memo": {}}
             body = np.broadcast_to(self.eval(k.red.body, ctx), shape2)
             if op in ("argmax", "argmin"):
                 part = self.reduce("max" if op == "argmax" else "min", body, len(D))
@@ -483,7 +488,7 @@ class Oracle:
             return False
         ops, subs = [], []
         for f in factors:
-            ctx = {"env": env, "ndim": len(allv), "stream": stream, "D": D, "lets": {}, "memo": {}}
+            ctx = {"env": env, "ndim": len(allv), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "memo": {}}
             val = np.asarray(self.eval(f, ctx))
             if val.ndim == 0:
                 val = val.reshape((1,) * len(allv))
@@ -551,7 +556,7 @@ class Oracle:
             return ctx["lets"][e.let.id]
         if k == "rand":                              # anvil/interp.py:549-559
             D = ctx["D"]
-            idx = np.int64(0)
+            idx = np.int64(ctx.get("rand_base", 0))
             for v, s in zip(D, kir.row_major_strides([v.extent for v in D])):
                 g = ctx["env"][v]
                 idx = idx + g.reshape(g.shape[:len(D)] + (1,) * (ctx["ndim"] - len(D))) * s

@@ -98,6 +98,24 @@ def do_configs():
         print(name, len(k.kernels()), "kernels")
 
 
+def do_dp():
+    """The same programs compiled for the global batch and for the per-rank batches of 2/4/8 ranks."""
+    from anvil.driver import compile_file
+    from anvil_lang_b200 import kir
+    jobs = [(os.path.join(ROOT, "tests", "programs", "dp_mlp.anvil"), HERE, "dp_mlp", 32, (1, 2, 4)),
+            (os.path.join(ROOT, "tests", "programs", "transformer_small.anvil"), HERE, "dp_transformer", 4, (1, 2)),
+            (os.path.join(ROOT, "anvil_lang_b200", "programs", "c5_transformer.anvil"),
+             os.path.join(ROOT, "anvil_lang_b200", "programs"), "c5_transformer", 64, (2, 4, 8)),
+            (os.path.join(ROOT, "anvil_lang_b200", "programs", "c3_mlp_adam.anvil"),
+             os.path.join(ROOT, "anvil_lang_b200", "programs"), "c3_mlp_adam", 256, (2, 4, 8))]
+    for path, outdir, name, batch, worlds in jobs:
+        for g in worlds:
+            c = compile_file(path, consts={"BATCH": batch // g})
+            k = kir.from_anvil(c.program, f"{name} (batch {batch // g})")
+            kir.dump(k, os.path.join(outdir, f"{name}.b{batch // g}.kir.json.gz"))
+            print(name, "batch", batch // g, len(k.kernels()), "kernels")
+
+
 def do_traj(name, steps, consts=None, suffix=""):
     """The first `steps` values of `loss` in the training loop, read after each iteration."""
     from anvil import ir
@@ -195,7 +213,7 @@ def do_functions():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["programs", "configs", "functions", "traj"])
+    ap.add_argument("what", choices=["programs", "configs", "functions", "traj", "dp"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--reference", default="/root/reference")
     a = ap.parse_args()
@@ -208,6 +226,8 @@ def main():
         do_configs()
     elif a.what == "functions":
         do_functions()
+    elif a.what == "dp":
+        do_dp()
     else:
         name, steps = a.args[0], int(a.args[1])
         consts = json.loads(a.args[2]) if len(a.args) > 2 else None

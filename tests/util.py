@@ -20,7 +20,8 @@ NUM = re.compile(r"-?\d+\.\d+(?:e[+-]?\d+)?|-?\d+(?:e[+-]?\d+)?|-?inf|nan")
 
 
 def golden_names():
-    return sorted(os.path.basename(p)[:-len(".kir.json.gz")] for p in glob.glob(os.path.join(GOLDEN, "*.kir.json.gz")))
+    names = sorted(os.path.basename(p)[:-len(".kir.json.gz")] for p in glob.glob(os.path.join(GOLDEN, "*.kir.json.gz")))
+    return [n for n in names if os.path.exists(os.path.join(GOLDEN, f"{n}.out.txt"))]
 
 
 def load_golden(name):
