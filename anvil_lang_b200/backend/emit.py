@@ -345,8 +345,9 @@ class KernelGen:
     def rand_index(self, scope: Scope, lane) -> str:
         strides = kir.row_major_strides([v.extent for v in self.k.domain])
         parts = [f"{s}u * (uint32_t){scope.var(v, lane)}" for v, s in zip(self.k.domain, strides)]
-        if self.k.rand_base:
-            parts.append(f"{self.k.rand_base & 0xFFFFFFFF}u")
+        if self.k.rand_base is not None:
+            rb, coef = self.k.rand_base
+            parts.append(f"{coef & 0xFFFFFFFF}u * (uint32_t){self.ptr(rb, False)}[0]")
         return " + ".join(parts) if parts else "0u"
 
     def pointer_decls(self) -> list[str]:

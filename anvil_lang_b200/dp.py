@@ -5,7 +5,8 @@ the single-GPU program: rank r of G runs the program compiled for the local batc
 `shard()` rewrites it so that
 
   1. batch gathers read rows  perm[B * step + r * b + i]  (the rank's slice of the global batch) and
-     the batch loop runs N / B times;
+     the batch loop runs N / B times; r is read at run time from a 0-d tensor, so all ranks run the
+     same compiled library;
   2. kernels that sample a step's inputs draw element r * b * rowlen + i of the global tensor
      (`Kernel.rand_base`), so the ranks' samples are slices of the single-GPU draw;
   3. every kernel that updates parameters or optimizer state is split at its reduction: the gradient
@@ -53,8 +54,10 @@ def _identity(domain) -> Affine:
     return Affine(0, list(zip(domain, strides)))
 
 
-def shard(prog: kir.Program, rank: int, world: int) -> kir.Program:
-    """Rewrites `prog` (compiled for the local batch) in place for rank `rank` of `world`."""
+def shard(prog: kir.Program, world: int) -> kir.Program:
+    """Rewrites `prog` (compiled for the local batch) in place for a run over `world` ranks. The
+    result is the same for every rank: the rank is a run-time value in the 0-d tensor
+    `prog.rank_buf`, which the caller sets (`DeviceProgram.set_rank`)."""
     if world == 1:
         return prog
     hot = an.hot_loop(prog)
@@ -62,6 +65,9 @@ def shard(prog: kir.Program, rank: int, world: int) -> kir.Program:
         raise ShardError("the program has no training loop")
     ids = itertools.count(max([b.id for b in prog.buffers] + [k.id for k in prog.kernels()]) + 1000)
     inv = 1.0 / world
+    rank_buf = kir.Buffer(next(ids), "dp.rank", (), kir.I32, "var")
+    prog.buffers.append(rank_buf)
+    prog.rank_buf = rank_buf
 
     # ---- 1, 2: the step's inputs
     producers, _ = an.input_producers(prog, hot)
@@ -69,14 +75,14 @@ def shard(prog: kir.Program, rank: int, world: int) -> kir.Program:
     for k in producers:
         b_local = k.domain[0].extent
         if k.uses_rand():
-            k.rand_base = rank * b_local * kir.prod(v.extent for v in k.domain[1:])
+            k.rand_base = (rank_buf, b_local * kir.prod(v.extent for v in k.domain[1:]))
             continue
         for e in [n for x in k.exprs() for n in x.walk() if n.k == "load"]:
             for g, _ in e.off.gathers():
                 srefs = g.offset.scalars()
                 if len(srefs) == 1 and srefs[0][0].buf.root is hot.counter.root:
                     terms = [(t, c * world if isinstance(t, kir.SRef) else c) for t, c in g.offset.terms]
-                    g.offset = Affine(g.offset.const + rank * b_local, terms)
+                    g.offset = Affine(g.offset.const, terms + [(kir.SRef(rank_buf), b_local)])
                     e._key = None
                     gathers_fixed = True
     if gathers_fixed:
@@ -187,3 +193,41 @@ def shard(prog: kir.Program, rank: int, world: int) -> kir.Program:
     hot.body.stmts = ([KernelStmt(k) for k in first] + [kir.AllReduce(bucket)]
                       + [KernelStmt(k) for k in tail + updates] + prints)
     return prog
+
+
+# ----------------------------------------------------------------------------- the collective on GPUs
+_keep = []          # ctypes callbacks must outlive the programs that hold them
+
+
+def attach(devprog, device: int):
+    """Binds a sharded `DeviceProgram` to the default `torch.distributed` process group (NCCL): the
+    program runs on a torch-owned stream, and its `kir.AllReduce` becomes `dist.all_reduce(SUM)` on
+    a tensor that aliases the arena's gradient bucket (in place, no staging copy)."""
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+    stream = torch.cuda.Stream(device=device)
+    devprog._check(devprog.rtlib.anvil_rt_use_stream(devprog.rt, ctypes.c_void_p(stream.cuda_stream)))
+    views = {}
+
+    class _Span:
+        def __init__(self, ptr, count):
+            self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+    def allreduce(user, ptr, count, cuda_stream):
+        try:
+            t = views.get((ptr, count))
+            if t is None:
+                t = views[(ptr, count)] = torch.as_tensor(_Span(ptr, count), device=f"cuda:{device}")
+            with torch.cuda.stream(stream):
+                dist.all_reduce(t)
+            return 0
+        except Exception as e:          # no exceptions across the C boundary
+            import sys
+            print(f"anvil: all-reduce failed: {e}", file=sys.stderr)
+            return 1
+    cb = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p)(allreduce)
+    _keep.append((cb, stream, views))
+    devprog.rtlib.anvil_rt_set_allreduce(devprog.rt, ctypes.cast(cb, ctypes.c_void_p), None)
+    return stream

@@ -35,8 +35,9 @@ def pinned_array(rtlib, shape, dtype) -> np.ndarray:
 class HostFeeder:
     """Prepares the inputs of training step `i` on the host and copies them to the device."""
 
-    def __init__(self, dp):
+    def __init__(self, dp, rank: int = 0):
         self.dp = dp
+        self.rank = rank
         self.hot = hot_loop(dp.prog)
         self.kernels, self.bufs = input_producers(dp.prog, self.hot)
         if not self.kernels:
@@ -60,20 +61,26 @@ class HostFeeder:
             m = e.a[0].a[0]
             if m.k == "bin" and m.op == "mul" and m.a[0].k == "const" and m.a[1].k == "rand" \
                     and m.a[1].salt == 0 and not m.a[1].open_low:
-                return {"mode": "randint", "hi": int(m.a[0].val), "shape": shape, "dtype": dtype, "buf": st.buf}
+                base = k.rand_base[1] * self.rank if k.rand_base is not None else 0
+                return {"mode": "randint", "hi": int(m.a[0].val), "shape": shape, "dtype": dtype, "buf": st.buf,
+                        "base": base}
         # batch rows: data[perm[B * counter + i], j...]
         if e.k == "load":
             gs = e.off.gathers()
             if len(gs) == 1 and not e.off.scalars():
                 g, row = gs[0]
-                srefs = g.offset.scalars()
+                rank_buf = getattr(self.dp.prog, "rank_buf", None)
+                all_srefs = g.offset.scalars()
+                rank_terms = [(t, c) for t, c in all_srefs if rank_buf is not None and t.buf.root is rank_buf.root]
+                srefs = [(t, c) for t, c in all_srefs if (t, c) not in rank_terms]
+                rank_mult = rank_terms[0][1] if rank_terms else 0
                 if len(srefs) == 1 and len(g.offset.var_terms()) == 1 and g.offset.var_terms()[0][0] is k.domain[0]:
                     rest = kir.Affine(e.off.const, e.off.var_terms())
                     lo_hi = rest.bounds()
                     inner = kir.prod(shape[1:])
                     if lo_hi == (0, inner - 1) and row == inner or (inner == 1 and row == 1):
                         return {"mode": "rows", "data": e.buf, "perm": g.buf, "counter": srefs[0][0].buf,
-                                "mult": srefs[0][1], "const": g.offset.const, "row": row,
+                                "mult": srefs[0][1], "const": g.offset.const + rank_mult * self.rank, "row": row,
                                 "shape": shape, "dtype": dtype, "buf": st.buf}
         raise Unsupported(f"{k.name}: not a batch gather or a token sampler")
 
@@ -90,7 +97,7 @@ class HostFeeder:
         s = stream
         for p, out in zip(self.plans, self.pinned):
             if p["mode"] == "randint":
-                out[...] = hostrng.randint(p["shape"], 0, p["hi"], s, seed)
+                out[...] = hostrng.randint(p["shape"], 0, p["hi"], s, seed, base=p["base"])
                 s += 1
             else:
                 B = p["shape"][0]

@@ -269,7 +269,8 @@ class Kernel:
     domain: list
     stmts: list
     red: Reduction | None = None
-    rand_base: int = 0     # added to the element index of every random draw (a rank's slice of a global tensor)
+    rand_base: object = None   # (i32 0-d Buffer, coef): coef * buffer value is added to the element index of
+                               # every random draw (a rank's slice of a global tensor)
 
     @property
     def stores(self):
@@ -430,6 +431,7 @@ class Program:
     buffers: list
     name: str = "<program>"
     bucket: list = field(default_factory=list)     # tensors an AllReduce sums: laid out contiguously
+    rank_buf: Buffer | None = None                 # i32 0-d: this process's rank in a data-parallel run
 
     def kernels(self) -> list[Kernel]:
         out = []

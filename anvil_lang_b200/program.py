@@ -67,6 +67,12 @@ class DeviceProgram:
         self.rtlib.anvil_rt_arena_bytes(self.rt)
         self._check(self.rtlib.anvil_rt_sync(self.rt))
 
+    def set_rank(self, rank: int):
+        """The rank of this process in a data-parallel run (after every `reset`)."""
+        if self.prog.rank_buf is not None:
+            self._check(self.rtlib.anvil_rt_set_i32(self.rt, self.plan.off(self.prog.rank_buf), int(rank)))
+            self._check(self.rtlib.anvil_rt_sync(self.rt))
+
     # ---- tensors
     def read(self, b: kir.Buffer) -> np.ndarray:
         out = np.empty(max(b.numel, 1), dtype=np.int32 if b.dtype == kir.I32 else np.float32)

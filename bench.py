@@ -174,7 +174,7 @@ def reference_arm(args, name, batch, desc):
     last["value"] = v
     line = {"impl": "reference", "metric": "train samples/s", "value": v, "unit": "samples/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * batch / v, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (program RNG, seed 0)",
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (program RNG, seed 0)",
             "config": {"workload": desc, "global_batch": batch}, "cpu_baseline": last,
             "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -195,17 +195,32 @@ def main():
     name, batch, desc = WORKLOADS[args.workload]
     if args.impl == "reference":
         return reference_arm(args, name, batch, desc)
-    if args.gpus > 1:
-        from anvil_lang_b200 import dp as dpmod
-        return dpmod.bench_main(args, name, batch, desc)
 
+    from anvil_lang_b200 import dp as dpmod
     from anvil_lang_b200 import kir
     from anvil_lang_b200.backend import analysis as an
     from anvil_lang_b200.feed import HostFeeder, Unsupported, pinned_array
     from anvil_lang_b200.program import DeviceProgram
 
-    prog = load_program(name)
-    dp = DeviceProgram(prog, seed=0, device=0)
+    world = int(os.environ.get("WORLD_SIZE", "1")) if args.gpus > 1 else 1
+    rank = int(os.environ.get("RANK", "0")) if world > 1 else 0
+    device = int(os.environ.get("LOCAL_RANK", "0")) if world > 1 else 0
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(device)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{device}"))
+        if batch % world:
+            raise SystemExit(f"global batch {batch} does not divide over {world} GPUs")
+        prog = dpmod.shard(load_program(f"{name}.b{batch // world}"), world)
+    else:
+        prog = load_program(name)
+
+    dp = DeviceProgram(prog, seed=0, device=device)
+    dp.set_rank(rank)
+    if world > 1:
+        dpmod.attach(dp, device)
     dp.rtlib.anvil_rt_capture(dp.rt, 1)                 # the program's own prints stay off stdout
     dp.prologue()
     loss = dp.buffer("loss")
@@ -214,13 +229,27 @@ def main():
     step_bytes = sum(an.kernel_bytes(k) for k in kernels)
     flush = step_bytes < 2 * L2_BYTES                   # working set may sit in L2: evict it between steps
     W, K = args.warmup, args.steps
+
+    def barrier():
+        dp.sync()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{device}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for _ in range(W):
         dp.step()
-    dp.sync()
+    barrier()
     dp.rtlib.anvil_rt_capture(dp.rt, 1)                 # (re)starting capture drops the text so far
 
-    # ---- device-resident steps, CUDA events on the program's stream
-    clocks = ClockSampler()
+    # ---- device-resident steps, CUDA events on the program's stream, max over ranks
+    clocks = ClockSampler(device) if rank == 0 else None
     launches0 = dp.launches
     t_wall = time.perf_counter()
     if not flush:
@@ -235,47 +264,55 @@ def main():
             dp.timer_begin()
             dp.step()
             ms += dp.timer_end()
+    barrier()
     wall = time.perf_counter() - t_wall
+    ms = max_over_ranks(ms)
     launches = dp.launches - launches0
     last_loss = float(dp.read(loss).reshape(-1)[0])
     value = batch * K / (ms * 1e-3)
 
     # ---- end to end: inputs from pinned host memory every step, loss back to the host every step
-    e2e = None
     try:
-        feeder = HostFeeder(dp)
+        feeder = HostFeeder(dp, rank)
         feeder.load_host_copies()
         host_loss = pinned_array(dp.rtlib, (1,), np.float32)
         seed = dp.seed
         counter = int(dp.read(hot.counter).reshape(-1)[0])
         stream = int(dp.rtlib.anvil_rt_get_stream(dp.rt))
-        for i in range(2):                               # warm the fed path (its own launch graph)
+
+        def fed_step(read_loss):
+            nonlocal counter, stream
             feeder.prepare(counter, stream, seed)
             feeder.push()
             dp.step_fed()
+            if read_loss:
+                dp.copy_out_async(host_loss.ctypes.data, loss, 4)
+                dp.sync()
             counter += hot.step
             stream += feeder.rand_streams
-        dp.sync()
+        for i in range(2):                               # warm the fed path (its own launch graphs)
+            fed_step(False)
+        barrier()
         t0 = time.perf_counter()
         for i in range(K):
-            feeder.prepare(counter, stream, seed)
-            feeder.push()
-            dp.step_fed()
-            dp.copy_out_async(host_loss.ctypes.data, loss, 4)
-            dp.sync()
-            counter += hot.step
-            stream += feeder.rand_streams
-        t_e2e = time.perf_counter() - t0
-        e2e = {"value": batch * K / t_e2e, "unit": "samples/s", "h2d_bytes_per_step": feeder.bytes_per_step,
-               "d2h_bytes_per_step": 4, "ms_per_step": 1e3 * t_e2e / K, "loss": float(host_loss[0])}
+            fed_step(True)
+        barrier()
+        t_e2e = max_over_ranks(time.perf_counter() - t0)
+        e2e = {"value": batch * K / t_e2e, "unit": "samples/s", "h2d_bytes_per_step": feeder.bytes_per_step * world,
+               "d2h_bytes_per_step": 4 * world, "ms_per_step": 1e3 * t_e2e / K, "loss": float(host_loss[0])}
     except Unsupported as e:
         e2e = {"value": None, "unit": "samples/s", "why": str(e)}
-    clk = clocks.stop()
+    clk = clocks.stop() if clocks is not None else None
 
-    # ---- the dominant kernel and its roofline
-    rows = []
-    for k in kernels:
-        rows.append((dp.time_kernel(k, 3), k))
+    # ---- the dominant kernel and its roofline (rank 0; a collective cannot be timed alone)
+    if dist is not None:
+        dist.barrier()
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
+    rows = [(dp.time_kernel(k, 3), k) for k in kernels]
     total_k = sum(r[0] for r in rows)
     top_ms, top = max(rows, key=lambda r: r[0])
     note = dp.gen.kernel_notes[dp.gen.kernel_index[top.id]]
@@ -297,20 +334,23 @@ def main():
                 "share_of_step": top_ms / total_k, "peak_source": peaks["source"]}
     classes = {}
     for t, k in rows:
-        c = dp.gen.kernel_notes[dp.gen.kernel_index[k.id]].split()[0]
+        c = " ".join(dp.gen.kernel_notes[dp.gen.kernel_index[k.id]].split()[:2])
         classes[c] = classes.get(c, 0.0) + t
     roof["step_ms_by_class"] = {c: round(v, 3) for c, v in sorted(classes.items(), key=lambda kv: -kv[1])}
 
-    cpu = None if args.no_cpu else cpu_sample(name, batch, budget_s=args.cpu_budget)
-    line = {"metric": "train samples/s", "value": value, "unit": "samples/s", "n_gpus": 1, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+    cpu = None if (args.no_cpu or world > 1) else cpu_sample(name, batch, budget_s=args.cpu_budget)
+    line = {"metric": "train samples/s", "value": value, "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic (the program's own seeded RNG, seed 0)",
-            "config": {"workload": desc, "global_batch": batch, "parallelism": "dp1",
+            "config": {"workload": desc, "global_batch": batch, "parallelism": f"dp{world}",
                        "l2": ("per-step traffic %.0f MB exceeds the 126 MB L2, no flush" % (step_bytes / 1e6)) if not flush
                        else "L2 flushed with a 256 MB write between timed steps"},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clk, "roofline": roof, "cpu_baseline": cpu,
             "wall_ms_per_step": 1e3 * wall / K, "last_loss": last_loss}
     print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     dp.close()
     return 0
 

@@ -159,6 +159,12 @@ class Oracle:
     def arr(self, b: kir.Buffer) -> np.ndarray:
         return self.mem[b.root.id]
 
+    def rand_base(self, k: kir.Kernel) -> int:
+        if k.rand_base is None:
+            return 0
+        b, coef = k.rand_base
+        return coef * int(self.arr(b)[0])
+
     def tensor(self, b: kir.Buffer) -> np.ndarray:
         return self.arr(b)[:b.numel].reshape(b.shape)
 
@@ -394,11 +400,11 @@ class Oracle:
             if chunk_red and R:
                 acc = self.reduce_chunked(k, D, R, stream)
             else:
-                ctx = {"env": env, "ndim": len(allv), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "memo": {}}
+                ctx = {"env": env, "ndim": len(allv), "stream": stream, "rand_base": self.rand_base(k), "D": D, "lets": {}, "memo": {}}
                 body = np.broadcast_to(self.eval(k.red.body, ctx), fullshape)
                 acc = self.reduce(k.red.op, body, len(D))
         denv = {v: env[v].reshape(env[v].shape[:len(D)]) for v in D}
-        sctx = {"env": denv, "ndim": len(D), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "acc": acc, "memo": {}}
+        sctx = {"env": denv, "ndim": len(D), "stream": stream, "rand_base": self.rand_base(k), "D": D, "lets": {}, "acc": acc, "memo": {}}
         for st in k.stmts:
             if isinstance(st, kir.Let):
                 sctx["lets"][st.id] = self.eval(st.value, sctx)
@@ -440,7 +446,7 @@ class Oracle:
             e = min(r0.extent, s + per)
             env2 = self.grid(D + R, {r0: (s, e)})
             shape2 = tuple(v.extent for v in D) + tuple((e - s) if v is r0 else v.extent for v in R)
-            ctx = {"env": env2, "ndim": len(D + R), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "memo": {}}
+            ctx = {"env": env2, "ndim": len(D + R), "stream": stream, "rand_base": self.rand_base(k), "D": D, "lets": {}, "memo": {}}
             body = np.broadcast_to(self.eval(k.red.body, ctx), shape2)
             if op in ("argmax", "argmin"):
                 part = self.reduce("max" if op == "argmax" else "min", body, len(D))
@@ -488,7 +494,7 @@ class Oracle:
             return False
         ops, subs = [], []
         for f in factors:
-            ctx = {"env": env, "ndim": len(allv), "stream": stream, "rand_base": k.rand_base, "D": D, "lets": {}, "memo": {}}
+            ctx = {"env": env, "ndim": len(allv), "stream": stream, "rand_base": self.rand_base(k), "D": D, "lets": {}, "memo": {}}
             val = np.asarray(self.eval(f, ctx))
             if val.ndim == 0:
                 val = val.reshape((1,) * len(allv))

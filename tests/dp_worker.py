@@ -20,9 +20,10 @@ def main():
     path, world, out_path = sys.argv[1], int(sys.argv[2]), sys.argv[3]
     rank = int(os.environ["RANK"])
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    prog = dp.shard(kir.load(path), rank, world)
+    prog = dp.shard(kir.load(path), world)
     out = io.StringIO()
     o = Oracle(prog, out=out, seed=0)
+    o.arr(prog.rank_buf)[0] = rank
 
     def allreduce(arrays):
         for a in arrays:

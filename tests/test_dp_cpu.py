@@ -56,7 +56,7 @@ def test_transformer_ranks_match_global_batch(tmp_path):
 
 def test_shard_structure():
     prog = kir.load(os.path.join(ROOT, "anvil_lang_b200", "programs", "c3_mlp_adam.b128.kir.json.gz"))
-    dp.shard(prog, 1, 2)
+    dp.shard(prog, 2)
     from anvil_lang_b200.backend.analysis import hot_loop
     hot = hot_loop(prog)
     kinds = [type(s).__name__ for s in hot.body.stmts]
