@@ -127,6 +127,8 @@ def do_traj(name, steps, consts=None, suffix=""):
     c = compile_file(path, consts=consts)
     k = kir.from_anvil(c.program, name)
     hot = hot_loop(k)
+    if consts:                      # a variant of a configuration: its IR travels with the losses
+        kir.dump(k, os.path.join(HERE, f"{name}{suffix}.traj.kir.json.gz"))
     loss = [b for b in c.program.buffers if b.name == "loss"][-1]
     losses, times = [], []
 
