@@ -138,6 +138,21 @@ typedef int (*anvil_allreduce_fn)(void *user, void *device_ptr, long count, void
 void anvil_rt_set_allreduce(anvil_rt *rt, anvil_allreduce_fn fn, void *user);
 int anvil_rt_allreduce(anvil_rt *rt, size_t off, long count);
 
+/* ---- column sums without allocation (no counterpart in the reference: its runtime allocates every
+ * tensor with cudaMallocManaged and has no entry point a caller could use under a no-allocation rule).
+ * out[j] = sum_i x[i * cols + j] for a row-major f32 matrix; x and out are device pointers supplied by
+ * the caller, the launch goes to `cuda_stream`. It is the split column reduction the compiler emits
+ * for bias gradients, with the partial sums kept in a fixed 4 MiB array inside the library instead of
+ * the arena's scratch region, so the call performs no cudaMalloc / cudaFree at all. For callers that
+ * must not allocate: plug-ins inside a framework that owns device memory through its own pool,
+ * processes with a memory budget fixed at start-up, latency-critical loops.
+ * Returns 0, 1 (bad arguments), 2 (cols x splits exceeds ANVIL_COLSUM_STATIC_MAX_PARTIALS), 3 (CUDA
+ * error); the reason is printed on stderr. Every GPU that loads the library holds the array until the
+ * process ends; all calls share it, so calls that overlap on the GPU race (calls on one stream are
+ * ordered). The first call on a device resolves the array's address: make it outside stream capture. */
+#define ANVIL_COLSUM_STATIC_MAX_PARTIALS (1 << 20)
+int anvil_colsum_f32_static(const float *x, long rows, long cols, float *out, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
