@@ -758,6 +758,7 @@ class KernelGen:
         S = 1
         if tiles * NB < 148 and K >= 256:
             S = max(1, min(148 // (tiles * NB), K // 128, 32))
+        S = max(S, (K + 4095) // 4096)           # one accumulation chain stays <= 4096 long (rounding, see the header)
         AK = "true" if c.a_kcontig else "false"
         BKC = "true" if ct._contig(c.b, c.kvars[-1]) else "false"
         src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (tcgen05 3xTF32, 128x{BN} tiles, split {S})"),

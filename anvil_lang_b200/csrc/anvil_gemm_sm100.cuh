@@ -10,8 +10,10 @@
 //              hi = x with the low 13 mantissa bits cleared (exactly a TF32 value) and lo = x - hi
 //              (exact in f32), and write both into shared memory in the tensor core's canonical
 //              K-major no-swizzle layout: 16-byte chunk (row r, k-chunk c) at  c * LBO + r * 16.
-//   warp 8     one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs (hi*lo, lo*hi, hi*hi) into
-//              the same TMEM accumulator and commits the stage's "empty" barrier.
+//   warp 8     one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs: hi*hi into the main TMEM
+//              accumulator, hi*lo and lo*hi into a second one (the tensor core rounds its accumulator
+//              toward zero at every accumulate, so the small terms are kept away from the large sum);
+//              then it commits the stage's "empty" barrier.
 //   warps 0-7  afterwards read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp), transpose
 //              32 x 32 blocks through shared memory so that consecutive lanes hold consecutive n, and
 //              run the kernel's statements (the epilogue functor) with coalesced stores.
@@ -145,7 +147,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -210,9 +212,12 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
             for (int j = 0; j < BK / 8; j++) {
                 const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_A, LBO_A), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
                 const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
-                mma_tf32(tmem, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
-                mma_tf32(tmem, dal, dbh, IDESC, 1u);
-                mma_tf32(tmem, dah, dbh, IDESC, 1u);
+                // The accumulator rounds toward zero on every accumulate, at the ulp of the running sum.
+                // The two correction products are ~2^-11 of the main one: they get an accumulator of
+                // their own (columns BN .. 2BN-1), so the main sum is rounded once per k-step, not thrice.
+                mma_tf32(tmem + BN, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
+                mma_tf32(tmem + BN, dal, dbh, IDESC, 1u);
+                mma_tf32(tmem, dah, dbh, IDESC, (kb | j) ? 1u : 0u);
             }
             mma_commit(empty(s));
         }
@@ -228,14 +233,16 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
         const int q = warp & 3;                                                  // TMEM lanes 32q .. 32q + 31
         constexpr int CHUNKS = BN / 32;
         for (int c = warp >> 2; c < CHUNKS; c += 2) {
-            uint32_t r[32];
-            if (ok && nkb > 0) tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
-            else {
+            uint32_t r[32], r2[32];
+            if (ok && nkb > 0) {
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(BN + 32 * c), r2);
+            } else {
 #pragma unroll
-                for (int i = 0; i < 32; i++) r[i] = 0u;
+                for (int i = 0; i < 32; i++) r[i] = r2[i] = 0u;
             }
 #pragma unroll
-            for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
             __syncwarp();
             const int n = n0 + 32 * c + lane;
             for (int rr = 0; rr < 32; rr++) {
@@ -253,7 +260,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     __syncthreads();
     if (warp == 8) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
     }
     if (t == 0 && *failed) atomicExch(status, TIMEOUT);
 }

@@ -24,6 +24,7 @@ CASES = [
     (256, 256, 64, 4, False, True, False, False, 1.0, False, False),
     (130, 70, 36, 2, True, True, True, False, 1.0, False, False),
     (1024, 1024, 1024, 1, False, False, True, False, 1.0, False, False),
+    (16384, 512, 2048, 1, False, False, True, False, 1.0, False, False),       # a transformer MLP product (A is 134 MB)
 ]
 
 
@@ -54,7 +55,8 @@ def run_case(case, tc):
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[:4])))
 def test_tensor_core_contraction(case):
     err, note = run_case(case, tc=True)
-    assert err < 1e-5, (err, note)
+    # the tensor core's accumulator rounds toward zero at each of the K/8 accumulates: the error grows with K
+    assert err < (1e-5 if case[2] <= 1024 else 3e-5), (err, note)
 
 
 @pytest.mark.parametrize("case", CASES[:8], ids=lambda c: "x".join(map(str, c[:4])))
