@@ -770,19 +770,19 @@ class KernelGen:
         launch = []
         if S == 1:
             kname = base
-            src += [f"__global__ void __launch_bounds__(288, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+            src += [f"__global__ void __launch_bounds__(544, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, 1>({fn}{{A}}, nullptr, {status});", "}"]
         else:
             kname = base + "_part"
             self.gen.need_scratch(4 * M * N * NB * S)
             soff = self.gen.plan.scratch_off
-            src += [f"__global__ void __launch_bounds__(288, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+            src += [f"__global__ void __launch_bounds__(544, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, {S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
         launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
                       f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
-        launch.append(f"{kname}<<<dim3({tiles}, {NB * S}), 288, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        launch.append(f"{kname}<<<dim3({tiles}, {NB * S}), 544, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
         if S > 1:
             fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
             launch.append(self.launch_line(base, fb_, 256))

@@ -4,17 +4,17 @@
 //   C[b, m, n] = epilogue(alpha * sum_k A[b, m, k] * B[b, k, n])        (same functor contract as
 //                                                                        anvil_gemm_simt.cuh)
 //
-// One CTA computes a 128 x BN tile. Nine warps:
-//   warps 0-7  "converters": read operand values through the generated functor (so prologues such as
+// One CTA computes a 128 x BN tile. Seventeen warps:
+//   warps 0-15 "converters" (two groups of eight that take alternate k blocks): read operand values through the generated functor (so prologues such as
 //              max(x, 0), scales and gathers cost nothing extra), split every f32 x into
 //              hi = x with the low 13 mantissa bits cleared (exactly a TF32 value) and lo = x - hi
 //              (exact in f32), and write both into shared memory in the tensor core's canonical
 //              K-major no-swizzle layout: 16-byte chunk (row r, k-chunk c) at  c * LBO + r * 16.
-//   warp 8     one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs: hi*hi into the main TMEM
+//   warp 16    one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs: hi*hi into the main TMEM
 //              accumulator, hi*lo and lo*hi into a second one (the tensor core rounds its accumulator
 //              toward zero at every accumulate, so the small terms are kept away from the large sum);
 //              then it commits the stage's "empty" barrier.
-//   warps 0-7  afterwards read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp), transpose
+//   warps 0-15 afterwards read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp), transpose
 //              32 x 32 blocks through shared memory so that consecutive lanes hold consecutive n, and
 //              run the kernel's statements (the epilogue functor) with coalesced stores.
 // A 3-stage ring of {A hi, A lo, B hi, B lo} tiles (64.5 KB per stage at BN = 128) is handed back
@@ -34,7 +34,7 @@ namespace anvil {
 namespace tc {
 
 constexpr int BM = 128, BK = 32, STAGES = 3;
-constexpr int CONV_THREADS = 256, THREADS = 288;
+constexpr int CONV_THREADS = 256, CONV_GROUPS = 2, MMA_WARP = 16, THREADS = 544;
 constexpr uint32_t TIMEOUT = 0x7C05u;
 
 __host__ __device__ constexpr uint32_t lbo_bytes(int rows) { return (uint32_t)rows * 16u + 16u; }   // +16: no bank aliasing between k-chunks
@@ -146,7 +146,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -155,8 +155,12 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    if (warp < 8) {
+    if (warp < MMA_WARP) {
         // ---------------------------------------------------------------- converters
+        // Two groups of 8 warps take alternate k blocks, so one group's global loads are in flight
+        // while the other converts and stores.
+        const int grp = warp >> 3;
+        const int t = threadIdx.x & (CONV_THREADS - 1);
         float va[BM / 32][4], vb[BN / 32][4];
         auto fetch = [&](int k0) {
 #pragma unroll
@@ -176,8 +180,8 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
                 else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
             }
         };
-        if (nkb > 0) fetch(k_begin);
-        for (int kb = 0; kb < nkb; kb++) {
+        if (grp < nkb) fetch(k_begin + grp * BK);
+        for (int kb = grp; kb < nkb; kb += CONV_GROUPS) {
             const int s = kb % STAGES;
             const uint32_t ph = (kb / STAGES) & 1;
             if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
@@ -194,7 +198,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
                 TileMap<BKC, BN>::at(t, p, row, kc);
                 split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
             }
-            if (kb + 1 < nkb) fetch(k_begin + (kb + 1) * BK);      // next block's loads fly during the wait below
+            if (kb + CONV_GROUPS < nkb) fetch(k_begin + (kb + CONV_GROUPS) * BK);   // this group's next block: loads fly during the wait
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(full(s));
         }
@@ -225,14 +229,14 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     }
 
     // ---------------------------------------------------------------- epilogue
-    if (warp < 8) {
+    if (warp < MMA_WARP) {
         const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
         if (!ok) *failed = 1;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);    // this warp's 32 x 32 transpose block
         const int q = warp & 3;                                                  // TMEM lanes 32q .. 32q + 31
         constexpr int CHUNKS = BN / 32;
-        for (int c = warp >> 2; c < CHUNKS; c += 2) {
+        for (int c = warp >> 2; c < CHUNKS; c += MMA_WARP / 4) {
             uint32_t r[32], r2[32];
             if (ok && nkb > 0) {
                 tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
@@ -258,7 +262,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
     }
