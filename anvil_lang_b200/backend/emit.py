@@ -765,19 +765,23 @@ class KernelGen:
                f"struct {fn} {{", "    char *__restrict__ A;",
                f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = {NB};",
                f"    static constexpr float ALPHA = {flit(c.alpha)};"] + fa4 + fb4 + fe + ["};"]
-        smem = f"anvil::tc::smem_bytes({BN})"
+        # A in tensor memory pays off when A is read along m (lane = row gives coalesced loads); a
+        # k-contiguous A is read faster by the shared-memory variant's 8-lanes-per-row mapping
+        ts = tc_variant(c.a_kcontig) == "ts"
+        smem = f"anvil::tc::ts_smem_bytes({BN})" if ts else f"anvil::tc::smem_bytes({BN})"
+        tile_fn = f"anvil::tc::gemm_tc_ts_tile<{fn}, {BKC}, {BN}, " if ts else f"anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, "
         status = "(uint32_t *)(A + ANVIL_RT_STATUS_OFF)"
         launch = []
         if S == 1:
             kname = base
             src += [f"__global__ void __launch_bounds__(544, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
-                    f"    anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, 1>({fn}{{A}}, nullptr, {status});", "}"]
+                    f"    {tile_fn}1>({fn}{{A}}, nullptr, {status});", "}"]
         else:
             kname = base + "_part"
             self.gen.need_scratch(4 * M * N * NB * S)
             soff = self.gen.plan.scratch_off
             src += [f"__global__ void __launch_bounds__(544, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
-                    f"    anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, {S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
+                    f"    {tile_fn}{S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
         launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
@@ -786,7 +790,7 @@ class KernelGen:
         if S > 1:
             fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
             launch.append(self.launch_line(base, fb_, 256))
-        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}"
+        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}" + (" A-tmem" if ts else "")
         self.contraction = c
         return "\n".join(src), launch
 
@@ -794,6 +798,15 @@ class KernelGen:
 def use_tensor_cores() -> bool:
     import os
     return os.environ.get("ANVIL_B200_TC", "1") != "0"
+
+
+def tc_variant(a_kcontig: bool) -> str:
+    """"ts": A tiles in tensor memory; "ss": both operands in shared memory. ANVIL_B200_TC=ss|ts forces one."""
+    import os
+    v = os.environ.get("ANVIL_B200_TC", "1")
+    if v in ("ss", "ts"):
+        return v
+    return "ss" if a_kcontig else "ts"
 
 
 def index_t(n: int) -> str:

@@ -269,5 +269,193 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     if (t == 0 && *failed) atomicExch(status, TIMEOUT);
 }
 
+
+// ---------------------------------------------------------------------------- A operand in tensor memory
+// The same product with the A tiles kept in TMEM instead of shared memory. A kind::tf32 MMA of
+// 128 x 128 x 8 reads 4 KB of A and 4 KB of B; with both in shared memory the three MMAs per k-step
+// plus the converters' own stores ask for more than the 128 B/clk a shared memory delivers, and the
+// tensor pipe waits. Converter threads hold A values in registers anyway (lane = row), so they write
+// hi and lo straight into TMEM with tcgen05.st (lane = row, column = k) and the MMA takes A from
+// there; shared memory then carries B only.
+//
+// TMEM columns (512 allocated): [0, BN) main accumulator, [BN, 2BN) correction accumulator,
+// then per stage 64 columns: A hi (32 k) and A lo (32 k).
+constexpr int TS_STAGES = 4;
+__host__ __device__ constexpr uint32_t ts_stage_bytes(int bn) { return 2 * tile_bytes(bn); }
+// At least 116 KB, so that two CTAs never share an SM: each allocates all 512 TMEM columns.
+__host__ __device__ constexpr uint32_t ts_smem_bytes(int bn) {
+    return (TS_STAGES * ts_stage_bytes(bn) > 116u * 1024u ? TS_STAGES * ts_stage_bytes(bn) : 116u * 1024u) + 256;
+}
+
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+template <class F, bool BKC, int BN, int SPLIT>
+__device__ __forceinline__ void gemm_tc_ts_tile(const F &f, float *__restrict__ partial, uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int M = F::M, N = F::N, K = F::K;
+    constexpr int TILES_N = (N + BN - 1) / BN;
+    constexpr uint32_t LBO_B = lbo_bytes(BN), TB = tile_bytes(BN), STAGE = ts_stage_bytes(BN);
+    constexpr uint32_t BAR_OFF = ts_smem_bytes(BN) - 256;
+    constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK - 1) / BK * BK;
+    constexpr uint32_t A_COLS = 2 * BN;                       // first TMEM column of the A stages
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile_m = blockIdx.x / TILES_N, tile_n = blockIdx.x % TILES_N;
+    const int bt = SPLIT > 1 ? blockIdx.y / SPLIT : blockIdx.y;
+    const int sp = SPLIT > 1 ? blockIdx.y % SPLIT : 0;
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
+    const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
+    const int nkb = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFF);               // full[4], empty[4], accum
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + BAR_OFF + 96);
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + BAR_OFF + 104);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (TS_STAGES + s); };
+    const uint32_t accum = bar0 + 8u * (2 * TS_STAGES);
+
+    if (tid == 0) {
+        for (int s = 0; s < TS_STAGES; s++) { mbar_init(full(s), CONV_THREADS); mbar_init(empty(s), 1); }
+        mbar_init(accum, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < MMA_WARP) {
+        // ---------------------------------------------------------------- converters
+        const int grp = warp >> 3, wi = warp & 7;
+        const int t = tid & (CONV_THREADS - 1);
+        const int q = wi & 3, half = wi >> 2;                 // A: TMEM lanes 32q.., k 16*half .. 16*half + 15
+        const int am = m0 + 32 * q + lane;
+        float va[4][4], vb[BN / 32][4];
+        auto fetch = [&](int k0) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int k = k0 + 16 * half + 4 * i;
+                if (am < M && k < k_end) f.a4(am, k, bt, va[i]);
+                else { va[i][0] = va[i][1] = va[i][2] = va[i][3] = 0.0f; }
+            }
+#pragma unroll
+            for (int p = 0; p < BN / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BN>::at(t, p, row, kc);
+                const int n = n0 + row, k = k0 + kc * 4;
+                if (n < N && k < k_end) f.b4(k, n, bt, vb[p]);
+                else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+            }
+        };
+        if (grp < nkb) fetch(k_begin + grp * BK);
+        for (int kb = grp; kb < nkb; kb += CONV_GROUPS) {
+            const int s = kb % TS_STAGES;
+            const uint32_t ph = (kb / TS_STAGES) & 1;
+            if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t hi[16], lo[16];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const uint32_t h = __float_as_uint(va[i][e]) & 0xFFFFE000u;
+                    hi[4 * i + e] = h;
+                    lo[4 * i + e] = __float_as_uint(va[i][e] - __uint_as_float(h));
+                }
+            const uint32_t a_base = tmem + ((uint32_t)(32 * q) << 16) + A_COLS + 64u * s + 16u * half;
+            tmem_st16(a_base, hi);
+            tmem_st16(a_base + 32u, lo);
+            uint8_t *st = smem + s * STAGE;
+#pragma unroll
+            for (int p = 0; p < BN / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BN>::at(t, p, row, kc);
+                split_store(st, st + TB, kc * LBO_B + row * 16, vb[p]);
+            }
+            if (kb + CONV_GROUPS < nkb) fetch(k_begin + (kb + CONV_GROUPS) * BK);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(full(s));
+        }
+    } else if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr uint32_t IDESC = instr_desc(BM, BN);
+        const uint32_t base = smem_u32(smem);
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % TS_STAGES;
+            const uint32_t ph = (kb / TS_STAGES) & 1;
+            if (!mbar_wait(full(s), ph)) { *failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t b_hi = base + s * STAGE, b_lo = b_hi + TB;
+            const uint32_t a_hi = tmem + A_COLS + 64u * s, a_lo = a_hi + 32u;
+#pragma unroll
+            for (int j = 0; j < BK / 8; j++) {
+                const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
+                mma_tf32_ts(tmem + BN, a_hi + 8u * j, dbl, IDESC, (kb | j) ? 1u : 0u);
+                mma_tf32_ts(tmem + BN, a_lo + 8u * j, dbh, IDESC, 1u);
+                mma_tf32_ts(tmem, a_hi + 8u * j, dbh, IDESC, (kb | j) ? 1u : 0u);
+            }
+            mma_commit(empty(s));
+        }
+        mma_commit(accum);
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    if (warp < MMA_WARP) {
+        const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
+        if (!ok) *failed = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);
+        const int q = warp & 3;
+        constexpr int CHUNKS = BN / 32;
+        for (int c = warp >> 2; c < CHUNKS; c += MMA_WARP / 4) {
+            uint32_t r[32], r2[32];
+            if (ok && nkb > 0) {
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(BN + 32 * c), r2);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = r2[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
+            __syncwarp();
+            const int n = n0 + 32 * c + lane;
+            for (int rr = 0; rr < 32; rr++) {
+                const int m = m0 + 32 * q + rr;
+                const float v = stage_f[rr * 33 + lane];
+                if (m < M && n < N) {
+                    if (SPLIT > 1) partial[(((long)bt * SPLIT + sp) * M + m) * N + n] = v;
+                    else f.epi(m, n, bt, v * F::ALPHA);
+                }
+            }
+            __syncwarp();
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    if (tid == 0 && *failed) atomicExch(status, TIMEOUT);
+}
+
 }  // namespace tc
 }  // namespace anvil

@@ -29,8 +29,9 @@ CASES = [
 
 
 def run_case(case, tc):
+    """tc: True / "ts" (A tiles in tensor memory), "ss" (both operands in shared memory), False (CUDA cores)."""
     M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out = case
-    os.environ["ANVIL_B200_TC"] = "1" if tc else "0"
+    os.environ["ANVIL_B200_TC"] = {True: "1", "ts": "ts", "ss": "ss", False: "0"}[tc]
     try:
         prog, kern, A, B, C, bias_b = contraction_program(M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out)
         dp = DeviceProgram(prog, graphs=False)
@@ -52,9 +53,10 @@ def run_case(case, tc):
     return err, note
 
 
+@pytest.mark.parametrize("variant", ["ts", "ss"])
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[:4])))
-def test_tensor_core_contraction(case):
-    err, note = run_case(case, tc=True)
+def test_tensor_core_contraction(case, variant):
+    err, note = run_case(case, tc=variant)
     # the tensor core's accumulator rounds toward zero at each of the K/8 accumulates: the error grows with K
     assert err < (1e-5 if case[2] <= 1024 else 3e-5), (err, note)
 
