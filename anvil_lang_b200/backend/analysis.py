@@ -227,3 +227,22 @@ def input_producers(prog: kir.Program, hot: kir.For):
         ks.append(k)
         bufs += [s.buf.root for s in k.stores]
     return ks, bufs
+
+
+def group_bytes(kernels, dead=()) -> int:
+    """Compulsory traffic of a fused run of kernels: every tensor that comes from outside the run is
+    read once, every tensor that outlives it is written once; what stays in registers moves nothing."""
+    written, read, total = set(), {}, 0
+    for k in kernels:
+        dom, red = k.out_numel(), k.red_numel()
+        for e, n in ([(k.red.body, dom * red)] if k.red is not None else []) + [(st.value, dom) for st in k.stmts]:
+            for x in e.walk():
+                if x.k == "load" and x.buf.root.id not in written:
+                    r = x.buf.root
+                    read[r.id] = max(read.get(r.id, 0), min(r.numel, n))
+        for st in k.stores:
+            r = st.buf.root
+            if r.id not in written and r.id not in dead:
+                total += 4 * dom
+            written.add(r.id)
+    return total + 4 * sum(read.values())

@@ -32,6 +32,7 @@ from .. import kir
 from ..kir import F32, I32
 from . import analysis as an
 from . import contraction as ct
+from . import rowgroup as rg
 
 THREADS = 256
 MAX_BLOCKS = 148 * 8
@@ -86,7 +87,7 @@ class Scope:
         self.memo: dict = {}
         self.dep: dict = {}
         self.lets: dict = {}            # let id -> {lane: code}
-        self.rand_idx = None            # C expression of the row-major domain index (per lane: callable)
+        self.acc_name = "acc"           # C identifier that holds the kernel's reduction result
 
     # ---- which nodes vary along the vectorised var
     def off_depends(self, a: kir.Affine) -> bool:
@@ -163,7 +164,7 @@ class Scope:
         if e.k == "const":
             return flit(e.val) if e.dt == F32 else f"({int(e.val)})"
         if e.k == "acc":
-            return "acc"
+            return self.acc_name
         if e.k == "let":
             d = self.lets[e.let.id]
             return d[lane if d["dep"] else None]
@@ -204,14 +205,15 @@ class Scope:
 
     def load(self, e: kir.E, lane) -> str:
         p = self.kg.ptr(e.buf, False)
-        if self.lanes == 4 and self.depends(e) and an.stride_of(e.off, self.vv) == 1 and an.aligned4(e.off, self.vv):
-            vkey = ("vec", e.key())
+        if self.lanes % 4 == 0 and self.lanes >= 4 and self.depends(e) and an.stride_of(e.off, self.vv) == 1 \
+                and an.aligned4(e.off, self.vv):
+            vkey = ("vec", e.key(), lane // 4)           # lanes come in aligned groups of 4 consecutive elements
             q = self.memo.get(vkey)
             if q is None:
                 q = self.kg.tmp("q")
-                self.emit(f"const {ctype(e.dt)}4 {q} = anvil::ld4({p} + ({self.affine(e.off, 0)}));")
+                self.emit(f"const {ctype(e.dt)}4 {q} = anvil::ld4({p} + ({self.affine(e.off, lane - lane % 4)}));")
                 self.memo[vkey] = q
-            return f"{q}.{'xyzw'[lane]}"
+            return f"{q}.{'xyzw'[lane % 4]}"
         return f"{p}[{self.affine(e.off, lane)}]"
 
     def unary(self, e: kir.E, lane) -> str:
@@ -287,19 +289,21 @@ class Scope:
         k, L = self.kg.k, self.lanes
         p = self.kg.ptr(st.buf, True)
         dt = st.buf.dtype
-        vec_ok = (L == 4 and an.stride_of(st.offset, self.vv) == 1 and an.aligned4(st.offset, self.vv))
+        vec_ok = (L % 4 == 0 and L >= 4 and an.stride_of(st.offset, self.vv) == 1 and an.aligned4(st.offset, self.vv))
         vals = [self.cast(st.value, dt, lane) for lane in range(L)]
         exclusive = an.exclusive_store(k, st)
         if vec_ok and (not st.accumulate or exclusive):
-            off = self.affine(st.offset, 0)
             T4 = f"{ctype(dt)}4"
-            if st.accumulate:
-                q = self.kg.tmp("q")
-                self.emit(f"{T4} {q} = anvil::ld4({p} + ({off}));")
-                self.emit(f"{q}.x += {vals[0]}; {q}.y += {vals[1]}; {q}.z += {vals[2]}; {q}.w += {vals[3]};")
-                self.emit(f"anvil::st4({p} + ({off}), {q});")
-            else:
-                self.emit(f"anvil::st4({p} + ({off}), make_{T4}({', '.join(vals)}));")
+            for g in range(0, L, 4):
+                off = self.affine(st.offset, g)
+                v = vals[g:g + 4]
+                if st.accumulate:
+                    q = self.kg.tmp("q")
+                    self.emit(f"{T4} {q} = anvil::ld4({p} + ({off}));")
+                    self.emit(f"{q}.x += {v[0]}; {q}.y += {v[1]}; {q}.z += {v[2]}; {q}.w += {v[3]};")
+                    self.emit(f"anvil::st4({p} + ({off}), {q});")
+                else:
+                    self.emit(f"anvil::st4({p} + ({off}), make_{T4}({', '.join(v)}));")
             return
         for lane in range(L):
             target = f"{p}[{self.affine(st.offset, lane)}]"
@@ -413,12 +417,15 @@ class KernelGen:
             return ("thread",)
         rlast = k.red.vars[-1]
         dlast = k.domain[-1] if k.domain else None
+        # which way do the loads that are re-read at every reduction step walk memory? (a load that
+        # does not depend on the reduction vars is one value per output: it does not count)
         row = col = 0
+        rset = set(k.red.vars)
         for n in k.red.body.walk():
-            if n.k == "load":
+            if n.k == "load" and rset & set(n.off.vars()):
                 if an.stride_of(n.off, rlast) == 1:
                     row += 1
-                if dlast is not None and an.stride_of(n.off, dlast) == 1:
+                elif dlast is not None and an.stride_of(n.off, dlast) == 1:
                     col += 1
         if dlast is None or row > col or ON == 1:
             L = self.vec_width_red()
@@ -795,6 +802,11 @@ class KernelGen:
         return "\n".join(src), launch
 
 
+def use_row_groups() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_ROWGROUPS", "1") != "0"
+
+
 def use_tensor_cores() -> bool:
     import os
     return os.environ.get("ANVIL_B200_TC", "1") != "0"
@@ -807,6 +819,158 @@ def tc_variant(a_kcontig: bool) -> str:
     if v in ("ss", "ts"):
         return v
     return "ss" if a_kcontig else "ts"
+
+
+class RowScope(Scope):
+    """Scope of one kernel inside a fused row group: loads of elements an earlier kernel of the
+    group produced come from registers, stores to tensors nothing else reads are dropped."""
+
+    def __init__(self, gg: "RowGroupGen", form, lanes, ind):
+        names = {}
+        if form.rowvar is not None:
+            names[form.rowvar] = "row"
+        names[form.jvar] = "cv" if form.collapsed else "j"
+        super().__init__(gg, names, lanes, form.jvar if lanes > 1 else None, ind)
+        self.gg = gg
+        self.form = form
+        self.scalar_stores: list[str] = []
+
+    def key(self, buf, off):
+        return (buf.root.id,) + tuple(self.form.canon(off))
+
+    def load(self, e: kir.E, lane) -> str:
+        key = self.key(e.buf, e.off)
+        hit = self.gg.fwd.get(key)
+        if hit is not None:
+            return hit[lane] if key[2] == 1 else hit[0]
+        return super().load(e, lane)
+
+    def store(self, st: kir.Store):
+        key = self.key(st.buf, st.offset)
+        L = self.lanes
+        vec = key[2] == 1
+        vals = [self.cast(st.value, st.buf.dtype, lane) for lane in (range(L) if vec else [0])]
+        if st.accumulate:                                # read-modify-write of the element this thread owns
+            prev = self.gg.fwd.get(key)
+            p = self.kg.ptr(st.buf, True)
+            out = []
+            for i, v in enumerate(vals):
+                old = prev[i] if prev is not None else f"{p}[{self.affine(st.offset, i)}]"
+                name = self.kg.tmp()
+                self.emit(f"const float {name} = ({old}) + ({v});")
+                out.append(name)
+            vals = out
+        else:
+            out = []
+            for v in vals:                               # name the value so later phases can reuse it
+                name = self.kg.tmp()
+                self.emit(f"const float {name} = {v};")
+                out.append(name)
+            vals = out
+        self.gg.fwd[key] = vals
+        if st.buf.root.id in self.gg.dead:
+            return
+        p = self.kg.ptr(st.buf, True)
+        if not vec:
+            self.emit(f"if (tt == 0 && live) {p}[{self.affine(st.offset, 0)}] = {vals[0]};")
+            return
+        self.emit("if (live) {")
+        if an.aligned4(st.offset, self.vv) and L % 4 == 0:
+            for g in range(0, L, 4):
+                self.emit(f"    anvil::st4({p} + ({self.affine(st.offset, g)}), make_float4({', '.join(vals[g:g + 4])}));")
+        else:
+            for lane in range(L):
+                self.emit(f"    {p}[{self.affine(st.offset, lane)}] = {vals[lane]};")
+        self.emit("}")
+
+
+class RowGroupGen:
+    """A fused row group (see rowgroup.py) -> one __global__ function and a launcher."""
+
+    def __init__(self, gen: "ProgramGen", forms, dead: set):
+        self.gen = gen
+        self.forms = forms
+        self.dead = dead
+        self.n = 0
+        self.ptrs: dict = {}
+        self.fwd: dict = {}              # (root, a, b, const) -> list of C identifiers
+        self.parallel = True
+        self.uses_rand = False
+        self.k = forms[0].kernel
+        self.written = set()
+        for f in forms:
+            self.written |= {s.buf.root.id for s in f.kernel.stores}
+
+    def tmp(self, prefix="t") -> str:
+        self.n += 1
+        return f"{prefix}{self.n}"
+
+    def ptr(self, b: kir.Buffer, write: bool) -> str:
+        r = b.root
+        self.ptrs[r.id] = (r, r.id in self.written)
+        return f"b{r.id}"
+
+    def rand_varies_with(self, vv) -> bool:
+        return False
+
+    def generate(self, name: str):
+        R, N = self.forms[0].R, self.forms[0].N
+        T = rg.threads_per_row(N)
+        E = N // T
+        RB = rg.THREADS // T
+        ind = "    "
+        body = []
+        for pi, f in enumerate(self.forms):
+            k = self.k = f.kernel
+            body.append(f"{ind}// ---- {k.name} <{k.label}>")
+            if f.kind == "red":
+                sc = RowScope(self, f, E, ind)
+                dep = sc.depends(k.red.body)
+                vals = [sc.ex(k.red.body, lane if dep else 0) for lane in range(E)]
+                body += sc.lines
+                OP = RED_OP[k.red.op]
+                acc = f"acc{pi}"
+                body.append(f"{ind}float {acc} = {OP}::id<float>();")
+                for v in vals:
+                    body.append(f"{ind}{acc} = {OP}::f({acc}, {v});")
+                body.append(f"{ind}{acc} = anvil::row_reduce<{OP}, {T}>({acc}, red_);")
+                tail = RowScope(self, f, 1, ind)
+                tail.acc_name = acc
+                tail.statements()
+                body += tail.lines
+            else:
+                sc = RowScope(self, f, E, ind)
+                sc.statements()
+                body += sc.lines
+        head = [f"// fused row group: {' + '.join(f.kernel.name for f in self.forms)} | {R} rows x {N} | "
+                f"{T} threads per row, {E} elements each",
+                f"__global__ void __launch_bounds__({rg.THREADS}) {name}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{"]
+        decls = []
+        for rid, (r, w) in sorted(self.ptrs.items()):
+            Tn = ctype(r.dtype)
+            off = self.gen.plan.offsets[rid]
+            if w:
+                decls.append(f"    {Tn} *b{rid} = ({Tn} *)(A + {off}UL);   // {r.name}{list(r.shape)}")
+            else:
+                decls.append(f"    const {Tn} *__restrict__ b{rid} = (const {Tn} *)(A + {off}UL);   // {r.name}{list(r.shape)}")
+        decls += [f"    __shared__ float red_[8];",
+                  f"    const int tt = threadIdx.x % {T};",
+                  f"    const long row_ = blockIdx.x * {RB}L + threadIdx.x / {T};",
+                  f"    const bool live = row_ < {R}L;",
+                  f"    const int row = (int)(live ? row_ : {R - 1}L);"]
+        wide = R * N >= (1 << 31)
+        for i in range(E):
+            decls.append(f"    const int j_{i} = ({i // 4} * {T} + tt) * 4 + {i % 4};")
+        if any(f.collapsed for f in self.forms):
+            ty = "long" if wide else "int"
+            for i in range(E):
+                decls.append(f"    const {ty} cv_{i} = ({ty})row * {N} + j_{i};")
+            decls.append(f"    const {'long' if wide else 'int'} cv = cv_0; (void)cv;")
+        decls.append("    const int j = j_0; (void)j;")
+        src = "\n".join(head + decls + body + ["}"])
+        blocks = (R + RB - 1) // RB
+        launch = [f"{name}<<<{blocks}, {rg.THREADS}, 0, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);"]
+        return src, launch
 
 
 def index_t(n: int) -> str:
@@ -836,6 +1000,99 @@ class ProgramGen:
         self.hot_body_fed: list[str] | None = None
         self.feed_bufs: list = []
         self.feed_kernels: list = []
+        self.groups: dict = {}                  # tuple of kernel ids -> launch-table index of the fused kernel
+        self.group_src: list[str] = []
+        self.group_launchers: list[str] = []
+        self.group_notes: list[str] = []
+        self.dead_roots: set = set()            # temporaries that live only in registers of a fused group (never stored)
+        self.hot_units: list = []               # (launch-table index, note, [kernels]) of the training loop, in order
+        self.record_units = False
+        self.readers: dict = {}
+        for k in prog.kernels():
+            for r in k.reads():
+                self.readers.setdefault(r.id, set()).add(k.id)
+        self.host_read = self._host_reads()
+
+    def _host_reads(self) -> set:
+        """Root ids of tensors that something other than a kernel reads."""
+        out = set()
+
+        def note(b):
+            if isinstance(b, kir.Buffer):
+                out.add(b.root.id)
+        for blk in kir.walk_blocks(self.prog.main):
+            for st in blk.stmts:
+                if isinstance(st, kir.For):
+                    note(st.counter); note(st.start); note(st.stop)
+                elif isinstance(st, kir.While):
+                    note(st.cond)
+                elif isinstance(st, kir.If):
+                    note(st.cond)
+                elif isinstance(st, kir.Print):
+                    for it in st.items:
+                        note(it.buf)
+                elif isinstance(st, kir.Check):
+                    for t, _ in st.value.scalars():
+                        note(t.buf)
+                elif isinstance(st, kir.RTCall):
+                    for v in st.args.values():
+                        note(v)
+                        if isinstance(v, list):
+                            for x in v:
+                                note(x)
+                elif isinstance(st, kir.AllReduce):
+                    for b in st.bufs:
+                        note(b)
+        for b in self.prog.buffers:
+            if b.root.kind not in ("temp", "grad"):
+                out.add(b.root.id)
+        return out
+
+    def add_group(self, kernels: list) -> int:
+        """Launch-table index of the fused kernel for this run of row kernels."""
+        key = tuple(k.id for k in kernels)
+        hit = self.groups.get(key)
+        if hit is not None:
+            return hit
+        forms, N = [], None
+        for k in kernels:
+            f = rg.row_form(k, N)
+            if f is None and N is None:
+                N = next(rg.row_form(x).N for x in kernels if rg.row_form(x) is not None)
+                f = rg.row_form(k, N)
+            N = f.N
+            forms.append(f)
+        ids = set(key)
+        dead = set()
+        written_so_far: dict = {}
+        order_ok: dict = {}
+        for f in forms:                                  # a tensor is private if every read follows a write of the same element
+            k = f.kernel
+            for b, off in k.loads():
+                r = b.root.id
+                if r not in written_so_far or f.canon(off) not in written_so_far[r]:
+                    order_ok[r] = False
+            for st in k.stores:
+                r = st.buf.root.id
+                if st.accumulate and (r not in written_so_far):
+                    order_ok[r] = False
+                written_so_far.setdefault(r, set()).add(f.canon(st.offset))
+        for r in written_so_far:
+            if r not in self.host_read and self.readers.get(r, set()) <= ids and order_ok.get(r, True):
+                dead.add(r)
+        self.dead_roots |= dead
+        gg = RowGroupGen(self, forms, dead)
+        name = f"g{len(self.groups)}_{kernels[0].id}"
+        src, launch = gg.generate(name)
+        idx = len(self.groups)
+        self.groups[key] = idx
+        self.group_src.append(src)
+        self.group_notes.append(f"rowgroup x{len(kernels)} {forms[0].R}x{forms[0].N}")
+        body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
+                "    uint32_t seed = anvil_rt_get_seed(rt);", "    uint32_t sdelta = 0;"] + ["    " + ln for ln in launch] + ["    return 0;"]
+        self.group_launchers.append(f"static int launch_group_{idx}(anvil_rt *rt) {{   // {' + '.join(k.name for k in kernels)}\n"
+                                    + "\n".join(body) + "\n}")
+        return idx
 
     def fault(self, message: str) -> int:
         if message in self.faults:
@@ -891,16 +1148,34 @@ class ProgramGen:
                 j = i
                 run = []
                 calls = []
+                run_kernels = []
                 while j < len(stmts) and isinstance(stmts[j], kir.KernelStmt):
                     kj = stmts[j].kernel
-                    idx = self.add_kernel(kj)
+                    self.add_kernel(kj)
                     if kj.id in skip:                # fed from the host; its random stream is still consumed
                         if kj.uses_rand():
                             calls.append("anvil_rt_set_stream(rt, anvil_rt_get_stream(rt) + 1u);")
                     else:
+                        run_kernels.append(kj)
+                    j += 1
+                spans = rg.find_groups(run_kernels) if use_row_groups() else []
+                starts = {a: b for a, b in spans}
+                q = 0
+                while q < len(run_kernels):
+                    if q in starts:
+                        ks = run_kernels[q:starts[q]]
+                        gi = self.add_group(ks)
+                        calls.append(f"RT(launch_group_{gi}(rt));")
+                        if self.record_units:
+                            self.hot_units.append((("g", gi), self.group_notes[gi], ks))
+                        q = starts[q]
+                    else:
+                        idx = self.kernel_index[run_kernels[q].id]
                         run.append(idx)
                         calls.append(f"RT(launch_{idx}(rt));")
-                    j += 1
+                        if self.record_units:
+                            self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
+                        q += 1
                 if j == len(stmts) and tail is not None:
                     calls += tail
                     tail_done = True
@@ -993,7 +1268,9 @@ class ProgramGen:
             is_hot = st is self.hot and not any(isinstance(s, kir.Break) for b in kir.walk_blocks(st.body) for s in b.stmts)
             body = self.block(st.body, ind + "        ", True, tail)
             if is_hot:
+                self.record_units = True
                 self.hot_body = self.block(st.body, "    ", True, tail)
+                self.record_units = False
                 feed_k, self.feed_bufs = an.input_producers(self.prog, st)
                 self.feed_kernels = feed_k
                 self.hot_body_fed = self.block(st.body, "    ", True, tail, skip={k.id for k in feed_k})
@@ -1093,12 +1370,17 @@ class ProgramGen:
         out += ["", "// ---------------------------------------------------------------- kernels"]
         for src in self.kernel_src:
             out += [src, ""]
+        for src in self.group_src:
+            out += [src, ""]
         out += ["// ---------------------------------------------------------------- launchers"]
-        out += self.launchers
-        n = len(self.kernels)
+        out += self.launchers + self.group_launchers
+        nk = len(self.kernels)
+        n = nk + len(self.groups)
         out += ["", "typedef int (*launch_fn)(anvil_rt *);",
-                "static const launch_fn launch_table[] = {" + ", ".join(f"launch_{i}" for i in range(n)) + ("0" if n == 0 else "") + "};",
-                f'extern "C" int anvil_b200_kernel_count(void) {{ return {n}; }}',
+                "static const launch_fn launch_table[] = {" + ", ".join([f"launch_{i}" for i in range(nk)]
+                                                                        + [f"launch_group_{i}" for i in range(len(self.groups))])
+                + ("0" if n == 0 else "") + "};",
+                f'extern "C" int anvil_b200_kernel_count(void) {{ return {nk}; }}',
                 f'extern "C" unsigned long anvil_b200_arena_bytes(void) {{ return {self.plan.size}UL; }}',
                 f'extern "C" unsigned int anvil_b200_seed(void) {{ return {self.seed}u; }}',
                 'extern "C" int anvil_b200_launch(anvil_rt *rt, int idx) {',

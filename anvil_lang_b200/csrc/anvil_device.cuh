@@ -93,6 +93,25 @@ ANVIL_DEV T block_reduce(T v, T *smem) {
     return warp_reduce<Op>(r);
 }
 
+// Reduction over the T threads that share one row (T a power of two, 32 <= T <= 256, rows packed
+// 256 / T to a CTA). Every thread of the row gets the result. Warps are combined in index order.
+// `smem` holds 8 floats. Must be reached by all threads of the CTA.
+template <typename Op, int T>
+ANVIL_DEV float row_reduce(float v, float *smem) {
+    v = warp_reduce<Op>(v);
+    if (T == 32) return v;
+    constexpr int WPR = T / 32;                      // warps per row
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) smem[w] = v;
+    __syncthreads();
+    const int w0 = (w / WPR) * WPR;
+    float r = smem[w0];
+#pragma unroll
+    for (int i = 1; i < WPR; i++) r = Op::f(r, smem[w0 + i]);
+    return r;
+}
+
 // argmax / argmin keep (value, flat reduction index); ties and equal values keep the smaller index,
 // which reproduces "first index of the strict extremum" (anvil/backend/cuda.py:286-307).
 template <typename T> struct Arg { T v; long i; };

@@ -312,10 +312,13 @@ def main():
             dist.barrier()
             dist.destroy_process_group()
         return 0
-    rows = [(dp.time_kernel(k, 3), k) for k in kernels]
+    nk = len(dp.gen.kernels)
+    rows = []                                            # (ms, note, kernels of the unit)
+    for (kind, idx), unote, ks in dp.gen.hot_units:
+        rows.append((dp.time_kernel(idx if kind == "k" else nk + idx, 3), unote, ks))
     total_k = sum(r[0] for r in rows)
-    top_ms, top = max(rows, key=lambda r: r[0])
-    note = dp.gen.kernel_notes[dp.gen.kernel_index[top.id]]
+    top_ms, note, top_ks = max(rows, key=lambda r: r[0])
+    top = top_ks[0]
     peaks = measured_peaks()
     if note.startswith("gemm"):
         tf32 = measure_tf32_peak()
@@ -327,14 +330,14 @@ def main():
                 "peak_source": "torch.matmul tf32 8192^3 best of 10, measured in this run, / 3 for 3xTF32" if tf32
                 else "fallback: half the bf16 fallback peak / 3"}
     else:
-        nbytes = an.kernel_bytes(top)
+        nbytes = an.group_bytes(top_ks, dp.gen.dead_roots)
         achieved = nbytes / (top_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": f"{top.name} {top.label} [{note}]",
                 "share_of_step": top_ms / total_k, "peak_source": peaks["source"]}
     classes = {}
-    for t, k in rows:
-        c = " ".join(dp.gen.kernel_notes[dp.gen.kernel_index[k.id]].split()[:2])
+    for t, unote, _ in rows:
+        c = " ".join(unote.split()[:2])
         classes[c] = classes.get(c, 0.0) + t
     roof["step_ms_by_class"] = {c: round(v, 3) for c, v in sorted(classes.items(), key=lambda kv: -kv[1])}
 

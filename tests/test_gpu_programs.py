@@ -30,7 +30,7 @@ def test_program_matches_reference(name, graphs):
         ok, why = outputs_match(got, text)
         assert ok, why
         rel = 2e-3 if name in TRAINED else 1e-4
-        bad = check_arrays(lambda b: dp.read(b).reshape(-1), prog, arrays, rel=rel)
+        bad = check_arrays(lambda b: dp.read(b).reshape(-1), prog, arrays, rel=rel, skip=dp.gen.dead_roots)
         assert not bad, bad
     finally:
         dp.close()

@@ -65,10 +65,11 @@ def tensor_close(got: np.ndarray, want: np.ndarray, rel=1e-4):
 
 
 def check_arrays(read, prog, arrays, rel=1e-4, skip=()):
-    """`read(buffer) -> flat array`; compares against what make_golden.py stored."""
+    """`read(buffer) -> flat array`; compares against what make_golden.py stored. `skip`: names or
+    root ids to leave out (temporaries that a fused kernel keeps in registers are never stored)."""
     bad = []
     for b in prog.roots():
-        if b.name in skip:
+        if b.name in skip or b.id in skip:
             continue
         full = arrays.get(f"b{b.id}_full")
         got = read(b)
