@@ -132,6 +132,10 @@ def match(k: kir.Kernel, min_flops: int = 1 << 21) -> Contraction | None:
         return None
     side_a, side_b, mvars, nvars, bvars = pick
     kvars = list(red.vars)
+    if kir.prod(v.extent for v in mvars) < 128 <= kir.prod(v.extent for v in nvars):
+        # which factor is called A is arbitrary: the tiles are 128 rows of M by 64 or 128 columns of N,
+        # so the short side goes to N
+        side_a, side_b, mvars, nvars = side_b, side_a, nvars, mvars
     c = Contraction(k, mvars, nvars, kvars, bvars, _product([ops[i] for i in side_a]),
                     _product([ops[i] for i in side_b]), alpha, False, False)
     if c.M < 32 or c.N < 32 or c.K < 8 or c.flops < min_flops:

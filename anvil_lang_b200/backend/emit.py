@@ -761,6 +761,7 @@ class KernelGen:
         fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
         fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
         BN = 128 if N >= 128 else 64
+
         tiles = ((M + 127) // 128) * ((N + BN - 1) // BN)
         S = 1
         if tiles * NB < 148 and K >= 256:
@@ -781,19 +782,19 @@ class KernelGen:
         launch = []
         if S == 1:
             kname = base
-            src += [f"__global__ void __launch_bounds__(544, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+            src += [f"__global__ void __launch_bounds__(anvil::tc::THREADS, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    {tile_fn}1>({fn}{{A}}, nullptr, {status});", "}"]
         else:
             kname = base + "_part"
             self.gen.need_scratch(4 * M * N * NB * S)
             soff = self.gen.plan.scratch_off
-            src += [f"__global__ void __launch_bounds__(544, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+            src += [f"__global__ void __launch_bounds__(anvil::tc::THREADS, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    {tile_fn}{S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
         launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
                       f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
-        launch.append(f"{kname}<<<dim3({tiles}, {NB * S}), 544, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        launch.append(f"{kname}<<<dim3({tiles}, {NB * S}), anvil::tc::THREADS, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
         if S > 1:
             fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
             launch.append(self.launch_line(base, fb_, 256))

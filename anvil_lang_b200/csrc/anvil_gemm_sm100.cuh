@@ -4,17 +4,17 @@
 //   C[b, m, n] = epilogue(alpha * sum_k A[b, m, k] * B[b, k, n])        (same functor contract as
 //                                                                        anvil_gemm_simt.cuh)
 //
-// One CTA computes a 128 x BN tile. Seventeen warps:
-//   warps 0-15 "converters" (two groups of eight that take alternate k blocks): read operand values through the generated functor (so prologues such as
+// One CTA computes a 128 x BN tile. Twenty-five warps:
+//   warps 0-23 "converters" (three groups of eight; group g takes k blocks g, g + 3, ...): read operand values through the generated functor (so prologues such as
 //              max(x, 0), scales and gathers cost nothing extra), split every f32 x into
 //              hi = x with the low 13 mantissa bits cleared (exactly a TF32 value) and lo = x - hi
 //              (exact in f32), and write both into shared memory in the tensor core's canonical
 //              K-major no-swizzle layout: 16-byte chunk (row r, k-chunk c) at  c * LBO + r * 16.
-//   warp 16    one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs: hi*hi into the main TMEM
+//   warp 24    one thread issues, per 32-wide k block, 4 k-steps x 3 MMAs: hi*hi into the main TMEM
 //              accumulator, hi*lo and lo*hi into a second one (the tensor core rounds its accumulator
 //              toward zero at every accumulate, so the small terms are kept away from the large sum);
 //              then it commits the stage's "empty" barrier.
-//   warps 0-15 afterwards read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp), transpose
+//   warps 0-23 afterwards read the accumulator (tcgen05.ld, 32 lanes x 32 columns per warp), transpose
 //              32 x 32 blocks through shared memory so that consecutive lanes hold consecutive n, and
 //              run the kernel's statements (the epilogue functor) with coalesced stores.
 // A 3-stage ring of {A hi, A lo, B hi, B lo} tiles (64.5 KB per stage at BN = 128) is handed back
@@ -34,13 +34,14 @@ namespace anvil {
 namespace tc {
 
 constexpr int BM = 128, BK = 32, STAGES = 3;
-constexpr int CONV_THREADS = 256, CONV_GROUPS = 2, MMA_WARP = 16, THREADS = 544;
+constexpr int CONV_THREADS = 256, CONV_GROUPS = 3, MMA_WARP = 8 * CONV_GROUPS, THREADS = 32 * MMA_WARP + 32;
 constexpr uint32_t TIMEOUT = 0x7C05u;
 
 __host__ __device__ constexpr uint32_t lbo_bytes(int rows) { return (uint32_t)rows * 16u + 16u; }   // +16: no bank aliasing between k-chunks
 __host__ __device__ constexpr uint32_t tile_bytes(int rows) { return (BK / 4) * lbo_bytes(rows); }
 __host__ __device__ constexpr uint32_t stage_bytes(int bn) { return 2 * tile_bytes(BM) + 2 * tile_bytes(bn); }
-__host__ __device__ constexpr uint32_t smem_bytes(int bn) { return STAGES * stage_bytes(bn) + 256; }
+__host__ __device__ constexpr int ss_stages(int bn) { return bn > 128 ? 2 : STAGES; }      // 227 KB of shared memory per CTA
+__host__ __device__ constexpr uint32_t smem_bytes(int bn) { return ss_stages(bn) * stage_bytes(bn) + 256; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -124,6 +125,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     constexpr uint32_t LBO_A = lbo_bytes(BM), LBO_B = lbo_bytes(BN);
     constexpr uint32_t TA = tile_bytes(BM), TB = tile_bytes(BN), STAGE = stage_bytes(BN);
     constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK - 1) / BK * BK;          // k range of one split
+    constexpr int NST = ss_stages(BN);
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int tile_m = blockIdx.x / TILES_N, tile_n = blockIdx.x % TILES_N;
     const int bt = SPLIT > 1 ? blockIdx.y / SPLIT : blockIdx.y;
@@ -132,16 +134,16 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
     const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
     const int nkb = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
 
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE);         // full[3], empty[3], accum
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + STAGES * STAGE + 64);
-    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + STAGES * STAGE + 72);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + NST * STAGE);         // full[3], empty[3], accum
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + NST * STAGE + 64);
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + NST * STAGE + 72);
     const uint32_t bar0 = smem_u32(bars);
     auto full = [&](int s) { return bar0 + 8u * s; };
-    auto empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
-    const uint32_t accum = bar0 + 8u * (2 * STAGES);
+    auto empty = [&](int s) { return bar0 + 8u * (NST + s); };
+    const uint32_t accum = bar0 + 8u * (2 * NST);
 
     if (t == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(full(s), CONV_THREADS); mbar_init(empty(s), 1); }
+        for (int s = 0; s < NST; s++) { mbar_init(full(s), CONV_THREADS); mbar_init(empty(s), 1); }
         mbar_init(accum, 1);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -157,8 +159,8 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
 
     if (warp < MMA_WARP) {
         // ---------------------------------------------------------------- converters
-        // Two groups of 8 warps take alternate k blocks, so one group's global loads are in flight
-        // while the other converts and stores.
+        // Groups of 8 warps take k blocks in turn, so one group's global loads are in flight while
+        // the others convert and store.
         const int grp = warp >> 3;
         const int t = threadIdx.x & (CONV_THREADS - 1);
         float va[BM / 32][4], vb[BN / 32][4];
@@ -182,8 +184,8 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
         };
         if (grp < nkb) fetch(k_begin + grp * BK);
         for (int kb = grp; kb < nkb; kb += CONV_GROUPS) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
+            const int s = kb % NST;
+            const uint32_t ph = (kb / NST) & 1;
             if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
             uint8_t *st = smem + s * STAGE;
 #pragma unroll
@@ -207,8 +209,8 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
         constexpr uint32_t IDESC = instr_desc(BM, BN);
         const uint32_t base = smem_u32(smem);
         for (int kb = 0; kb < nkb; kb++) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
+            const int s = kb % NST;
+            const uint32_t ph = (kb / NST) & 1;
             if (!mbar_wait(full(s), ph)) { *failed = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
