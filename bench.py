@@ -31,6 +31,9 @@ WORKLOADS = {
     "c1": ("c1_mlp_sgd", 64, "MLP 784-128-10, f32, cross_entropy, SGD lr 0.1, batch 64"),
 }
 L2_BYTES = 126 << 20
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under
+# profiles/ (gemm_tc_16384x512x2048.md), keyed by the kernel's strategy note
+NCU_TRAFFIC = {"gemm tc 1x16384x512x2048": 138.5e6 + 20.8e6}
 
 
 def load_program(name):
@@ -326,7 +329,7 @@ def main():
         achieved = flops / (top_ms * 1e-3) / 1e12
         peak = (tf32 / 3.0) if tf32 else 1590.0 / 2 / 3
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": None, "kernel": f"{top.name} {top.label} [{note}]", "share_of_step": top_ms / total_k,
+                "traffic": next((v for k_, v in NCU_TRAFFIC.items() if note.startswith(k_)), None), "kernel": f"{top.name} {top.label} [{note}]", "share_of_step": top_ms / total_k,
                 "peak_source": "torch.matmul tf32 8192^3 best of 10, measured in this run, / 3 for 3xTF32" if tf32
                 else "fallback: half the bf16 fallback peak / 3"}
     else:
