@@ -50,8 +50,29 @@ def parallel_safe(k: kir.Kernel) -> bool:
 
 
 def exclusive_store(k: kir.Kernel, s: kir.Store) -> bool:
-    """An accumulating store that no two output elements share: a plain read-modify-write."""
-    return not s.offset.gathers() and injective_over(s.offset, k.domain)
+    """An accumulating store that no two output elements share: a plain read-modify-write. A gathered
+    index whose checked range fits under the next larger stride (`out[10 * i + y[i]]`, y in [0, 10))
+    counts as one more digit of the mixed-radix argument."""
+    if s.offset.scalars():
+        return False
+    items = []
+    for v in k.domain:
+        if v.extent <= 1:
+            continue
+        c = s.offset.coef(v)
+        if c == 0:
+            return False
+        items.append((abs(c), v.extent))
+    for g, c in s.offset.gathers():
+        if c == 0 or g.hi <= g.lo:
+            return False
+        items.append((abs(c), g.hi - g.lo))
+    reach = 0
+    for c, n in sorted(items):
+        if c <= reach:
+            return False
+        reach += c * (n - 1)
+    return True
 
 
 def stride_of(off: kir.Affine, v: kir.Var) -> int | None:

@@ -88,6 +88,7 @@ class Scope:
         self.dep: dict = {}
         self.lets: dict = {}            # let id -> {lane: code}
         self.acc_name = "acc"           # C identifier that holds the kernel's reduction result
+        self.acc_lanes = False          # one result per lane (`acc_0` ...): lanes run along an output var
 
     # ---- which nodes vary along the vectorised var
     def off_depends(self, a: kir.Affine) -> bool:
@@ -105,7 +106,7 @@ class Scope:
             elif e.k == "let":
                 hit = self.lets.get(e.let.id, {}).get("dep", False)
             elif e.k == "acc":
-                hit = False
+                hit = self.acc_lanes
             else:
                 hit = any(self.depends(x) for x in e.a)
             self.dep[id(e)] = hit
@@ -164,7 +165,7 @@ class Scope:
         if e.k == "const":
             return flit(e.val) if e.dt == F32 else f"({int(e.val)})"
         if e.k == "acc":
-            return self.acc_name
+            return f"{self.acc_name}_{lane}" if self.acc_lanes else self.acc_name
         if e.k == "let":
             d = self.lets[e.let.id]
             return d[lane if d["dep"] else None]
@@ -200,7 +201,27 @@ class Scope:
             return self.binary(e, lane)
         if k == "sel":
             c = self.ex(e.a[0], lane)
-            return f"(({c}) != 0 ? {self.cast(e.a[1], e.dt, lane)} : {self.cast(e.a[2], e.dt, lane)})"
+            if not any(n.k == "load" for br in (e.a[1], e.a[2]) for n in br.walk()):
+                return f"(({c}) != 0 ? {self.cast(e.a[1], e.dt, lane)} : {self.cast(e.a[2], e.dt, lane)})"
+            # a branch that reads memory is only evaluated when taken (`x if hit else 0.0` inside a long
+            # reduction); with a condition shared by all lanes, one `if` serves all of them
+            shared = self.lanes > 1 and self.depends(e) and not self.depends(e.a[0])
+            lanes = list(range(self.lanes)) if shared else [lane]
+            names = {l: self.kg.tmp("s") for l in lanes}
+            self.emit(f"{ctype(e.dt)} " + ", ".join(names.values()) + ";")
+            for branch, head in ((e.a[1], f"if (({c}) != 0) {{"), (e.a[2], "} else {")):
+                self.emit(head)
+                saved = dict(self.memo)
+                self.ind += "    "
+                for l in lanes:
+                    self.emit(f"{names[l]} = {self.cast(branch, e.dt, l)};")
+                self.ind = self.ind[:-4]
+                self.memo = saved
+            self.emit("}")
+            for l in lanes:
+                if l != lane:
+                    self.memo[(e.key(), l)] = names[l]
+            return names[lane]
         raise NotImplementedError(k)
 
     def load(self, e: kir.E, lane) -> str:
@@ -434,6 +455,13 @@ class KernelGen:
             layout = "row"
         else:
             L, OX, RY, layout = 1, 32, 8, "col"
+            if k.red.body.dt == F32 and self.vec_width_domain() == 4:
+                groups = (ON // 4 + OX - 1) // OX         # each thread owns 4 consecutive outputs
+                S = 1
+                per_thread = RN // RY
+                if groups < 148 and per_thread >= 64:
+                    S = max(1, min(296 // groups, per_thread // 32, 64))
+                return ("coop4", OX, RY, S)
         blocks = (ON + OX - 1) // OX
         S = 1
         per_thread = RN // (RY * L)
@@ -489,6 +517,8 @@ class KernelGen:
             return self.gen_thread(base)
         if choice[0] == "gemm":
             return self.gen_gemm(base, choice[1])
+        if choice[0] == "coop4":
+            return self.gen_coop_col4(base, *choice[1:])
         return self.gen_coop(base, *choice[1:])
 
     def launch_line(self, name, blocks, threads) -> str:
@@ -673,6 +703,88 @@ class KernelGen:
         return "\n".join(part) + "\n\n" + "\n".join(final), launch
 
 
+    def gen_coop_col4(self, base, OX, RY, S):
+        """Column-layout cooperative reduction where every thread owns 4 consecutive outputs: 128-bit
+        loads along the output index, four accumulators, the same fixed trees as `gen_coop`."""
+        k = self.k
+        red = k.red
+        ON, RN = k.out_numel(), k.red_numel()
+        OP = RED_OP[red.op]
+        vv = k.domain[-1]
+        OG = ON // 4
+        nthreads = OX * RY
+        chunk = (RN + S - 1) // S
+        ind = "    "
+        lines = [f"{ind}const int ox = threadIdx.x % {OX}, ry = threadIdx.x / {OX};",
+                 f"{ind}const long o_ = blockIdx.x * {OX}L + ox;",
+                 f"{ind}const bool live = o_ < {OG}L;",
+                 f"{ind}const {index_t(OG)} u = ({index_t(OG)})(live ? o_ : {OG - 1}L);"]
+        lines += self.decode("u", k.domain, self.names, ind, vv, 4) + self.lane_vars(vv, 4, ind)
+        lines.append(f"{ind}float acc_0 = {OP}::id<float>(), acc_1 = acc_0, acc_2 = acc_0, acc_3 = acc_0;")
+        lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RN}L, rbeg + {chunk}L);")
+        lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
+        inner = ind + "    "
+        lines.append(f"{inner}const {index_t(RN)} rr = ({index_t(RN)})rr_;")
+        lines += self.decode("rr", red.vars, self.names, inner)
+        sc = Scope(self, self.names, 4, vv, inner)
+        dep = sc.depends(red.body)
+        vals = [sc.ex(red.body, lane if dep else 0) for lane in range(4)]
+        lines += sc.lines
+        for i, v in enumerate(vals):
+            lines.append(f"{inner}acc_{i} = {OP}::f(acc_{i}, {v});")
+        lines.append(f"{ind}}}")
+        lines.append(f"{ind}__shared__ float sm_[{RY}][{4 * OX + 4}];")
+        for i in range(4):
+            lines.append(f"{ind}sm_[ry][4 * ox + {i}] = acc_{i};")
+        lines.append(f"{ind}__syncthreads();")
+        s_ = RY // 2
+        while s_ >= 1:
+            lines.append(f"{ind}if (ry < {s_}) {{ " + " ".join(
+                f"sm_[ry][4 * ox + {i}] = {OP}::f(sm_[ry][4 * ox + {i}], sm_[ry + {s_}][4 * ox + {i}]);" for i in range(4)) + " }")
+            lines.append(f"{ind}__syncthreads();")
+            s_ //= 2
+        for i in range(4):
+            lines.append(f"{ind}acc_{i} = sm_[0][4 * ox + {i}];")
+        gx = (OG + OX - 1) // OX
+        launch = []
+        if S == 1:
+            tail = Scope(self, self.names, 4, vv, ind + "    ")
+            tail.acc_lanes = True
+            tail.statements()
+            lines.append(f"{ind}if (ry == 0 && live) {{")
+            lines += tail.lines
+            lines.append(f"{ind}}}")
+            src = [self.comment(f"cooperative reduction (col, {OX} x 4 outputs x {RY} threads)"),
+                   self.head(base, nthreads)] + self.pointer_decls() + lines + ["}"]
+            launch.append(self.launch_line(base, f"dim3({gx}, 1)", nthreads))
+            self.notes = f"coop col4 {OX}x{RY}"
+            return "\n".join(src), launch
+        self.gen.need_scratch(4 * ON * S)
+        soff = self.gen.plan.scratch_off
+        lines.append(f"{ind}if (ry == 0 && live) {{")
+        for i in range(4):
+            lines.append(f"{ind}    ((float *)(A + {soff}UL))[(o_ * 4 + {i}) * {S} + blockIdx.y] = acc_{i};")
+        lines.append(f"{ind}}}")
+        part = [self.comment(f"split reduction, part 1 of 2 (col, 4 outputs per thread, {S} CTAs per output group)"),
+                self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
+        saved = self.ptrs
+        self.ptrs = {}
+        fsc = Scope(self, self.names, 1, None, "        ")
+        fsc.statements()
+        fl = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {ON}L; tid += (long)gridDim.x * {THREADS}L) {{",
+              f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
+        fl += self.decode("u", k.domain, self.names, "        ")
+        fl.append(f"        float acc = {OP}::id<float>();")
+        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const float *)(A + {soff}UL))[tid * {S} + p]);")
+        final = [self.comment("split reduction, part 2 of 2"), self.head(base, THREADS)] + self.pointer_decls() \
+            + fl + fsc.lines + ["    }", "}"]
+        self.ptrs = {**saved, **self.ptrs}
+        launch.append(self.launch_line(base + "_part", f"dim3({gx}, {S})", nthreads))
+        fb = max(1, min((ON + THREADS - 1) // THREADS, MAX_BLOCKS))
+        launch.append(self.launch_line(base, fb, THREADS))
+        self.notes = f"split col4 {OX}x{RY} S{S}"
+        return "\n".join(part) + "\n\n" + "\n".join(final), launch
+
     # ---- contractions
     def functor_method(self, sig: str, decodes: list, build) -> list[str]:
         """One __device__ method of a contraction functor: index decode, pointers, body."""
@@ -801,6 +913,11 @@ class KernelGen:
         self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}" + (" A-tmem" if ts else "")
         self.contraction = c
         return "\n".join(src), launch
+
+
+def os_environ(name: str, default: str) -> str:
+    import os
+    return os.environ.get(name, default)
 
 
 def use_row_groups() -> bool:
@@ -1423,6 +1540,9 @@ class ProgramGen:
 def generate(prog: kir.Program, seed: int = 0):
     """Returns (source text, ProgramGen). Generated twice when split reductions need scratch space,
     because the scratch region sits in front of the buffers."""
+    if os_environ("ANVIL_B200_DETERMINISTIC", "1") != "0":
+        from .determinism import make_deterministic
+        make_deterministic(prog)                     # colliding `+=` get a fixed order (idempotent)
     g = ProgramGen(prog, seed)
     src = g.generate()
     if g.scratch_bytes > g.plan.scratch_bytes:

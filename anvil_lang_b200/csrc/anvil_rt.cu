@@ -157,6 +157,8 @@ extern "C" int anvil_rt_d2h_async(anvil_rt *rt, void *dst, size_t off, size_t by
 extern "C" int anvil_rt_zero(anvil_rt *rt, size_t off, size_t bytes) {
     if (in_range(rt, off, bytes)) return 1;
     CK(rt, cudaMemsetAsync(rt->arena + off, 0, bytes, rt->stream));
+    if (off <= ANVIL_RT_STREAM_OFF && off + bytes >= ANVIL_RT_STREAM_OFF + 4)
+        rt->pending = rt->host_stream;      // the device copy of the stream counter is 0 again
     return 0;
 }
 extern "C" int anvil_rt_sync(anvil_rt *rt) {
