@@ -872,12 +872,19 @@ class KernelGen:
         db = self.decode("(uint32_t)bt", c.bvars, self.names, ind) if c.bvars else []
         fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
         fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
-        BN = 128 if N >= 128 else 64
-
-        tiles = ((M + 127) // 128) * ((N + BN - 1) // BN)
+        variant = tc_variant(c.a_kcontig, M, N, K)
+        pair = variant == "pair"
+        if pair:                                 # 256 x BN tile per cluster of two CTAs
+            BN = 256 if N >= 256 else 128
+            tiles = ((M + 255) // 256) * ((N + BN - 1) // BN)
+            slots = 74
+        else:
+            BN = 128 if N >= 128 else 64
+            tiles = ((M + 127) // 128) * ((N + BN - 1) // BN)
+            slots = 148
         S = 1
-        if tiles * NB < 148 and K >= 256:
-            S = max(1, min(148 // (tiles * NB), K // 128, 32))
+        if tiles * NB < slots and K >= 256:
+            S = max(1, min(slots // (tiles * NB), K // 128, 32))
         S = max(S, (K + 4095) // 4096)           # one accumulation chain stays <= 4096 long (rounding, see the header)
         AK = "true" if c.a_kcontig else "false"
         BKC = "true" if ct._contig(c.b, c.kvars[-1]) else "false"
@@ -887,30 +894,42 @@ class KernelGen:
                f"    static constexpr float ALPHA = {flit(c.alpha)};"] + fa4 + fb4 + fe + ["};"]
         # A in tensor memory pays off when A is read along m (lane = row gives coalesced loads); a
         # k-contiguous A is read faster by the shared-memory variant's 8-lanes-per-row mapping
-        ts = tc_variant(c.a_kcontig) == "ts"
-        smem = f"anvil::tc::ts_smem_bytes({BN})" if ts else f"anvil::tc::smem_bytes({BN})"
-        tile_fn = f"anvil::tc::gemm_tc_ts_tile<{fn}, {BKC}, {BN}, " if ts else f"anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, "
+        ts = variant == "ts"
+        attrs = ""
+        if pair:
+            smem, threads, per_sm = f"anvil::tc::pair_smem_bytes({BN})", "anvil::tc::THREADS", 1
+            tile_fn = f"anvil::tc::gemm_tc_pair_tile<{fn}, {AK}, {BKC}, {BN}, "
+            attrs = "__cluster_dims__(2, 1, 1) "
+        elif ts:
+            smem, threads, per_sm = f"anvil::tc::ts_smem_bytes({BN})", "anvil::tc::THREADS", 1
+            tile_fn = f"anvil::tc::gemm_tc_ts_tile<{fn}, {BKC}, {BN}, "
+        elif variant == "ss32":
+            smem, threads, per_sm = f"anvil::tc::smem_bytes({BN})", "anvil::tc::THREADS", 1
+            tile_fn = f"anvil::tc::gemm_tc_tile<{fn}, {AK}, {BKC}, {BN}, "
+        else:
+            smem, threads, per_sm = f"anvil::tc::smem2_bytes({BN})", "anvil::tc::THREADS2", 2
+            tile_fn = f"anvil::tc::gemm_tc2_tile<{fn}, {AK}, {BKC}, {BN}, "
         status = "(uint32_t *)(A + ANVIL_RT_STATUS_OFF)"
         launch = []
         if S == 1:
             kname = base
-            src += [f"__global__ void __launch_bounds__(anvil::tc::THREADS, 1) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+            src += [f"__global__ void {attrs}__launch_bounds__({threads}, {per_sm}) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    {tile_fn}1>({fn}{{A}}, nullptr, {status});", "}"]
         else:
             kname = base + "_part"
             self.gen.need_scratch(4 * M * N * NB * S)
             soff = self.gen.plan.scratch_off
-            src += [f"__global__ void __launch_bounds__(anvil::tc::THREADS, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+            src += [f"__global__ void {attrs}__launch_bounds__({threads}, {per_sm}) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    {tile_fn}{S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
         launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
                       f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
-        launch.append(f"{kname}<<<dim3({tiles}, {NB * S}), anvil::tc::THREADS, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        launch.append(f"{kname}<<<dim3({2 * tiles if pair else tiles}, {NB * S}), {threads}, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
         if S > 1:
             fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
             launch.append(self.launch_line(base, fb_, 256))
-        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}" + (" A-tmem" if ts else "")
+        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}" + (" A-tmem" if ts else " pair" if pair else "")
         self.contraction = c
         return "\n".join(src), launch
 
@@ -930,13 +949,25 @@ def use_tensor_cores() -> bool:
     return os.environ.get("ANVIL_B200_TC", "1") != "0"
 
 
-def tc_variant(a_kcontig: bool) -> str:
-    """"ts": A tiles in tensor memory; "ss": both operands in shared memory. ANVIL_B200_TC=ss|ts forces one."""
+def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
+    """Which tcgen05 template a contraction takes (ANVIL_B200_TC=pair|ss|ss32|ts forces one where it applies):
+    "pair" two CTAs of a cluster share a 256 x 256 (or 256 x 128) tile, tcgen05.mma.cta_group::2 — needs
+           M >= 256 and N >= 128;
+    "ts"   A tiles in tensor memory — when A is read along m (measured 148-151 vs 124-130 TFLOP/s);
+    "ss"   operands in shared memory, 16-wide k blocks, two CTAs per SM — short reductions (K <= 128),
+           where a tile is mostly prologue and epilogue (QK^T-type products: 88 vs 73 TFLOP/s);
+    "ss32" operands in shared memory, 32-wide k blocks, one CTA per SM — everything else
+           (K = 2048: 134 vs 117 TFLOP/s for "ss")."""
     import os
     v = os.environ.get("ANVIL_B200_TC", "1")
-    if v in ("ss", "ts"):
+    pair_ok = M >= 256 and N >= 128
+    if v == "pair" and not pair_ok:
+        v = "1"
+    if v in ("pair", "ss", "ts", "ss32"):
         return v
-    return "ss" if a_kcontig else "ts"
+    if not a_kcontig:
+        return "ts"
+    return "ss" if K <= 128 else "ss32"
 
 
 class RowScope(Scope):

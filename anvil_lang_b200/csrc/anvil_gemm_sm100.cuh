@@ -459,5 +459,398 @@ __device__ __forceinline__ void gemm_tc_ts_tile(const F &f, float *__restrict__ 
     if (tid == 0 && *failed) atomicExch(status, TIMEOUT);
 }
 
+
+// ---------------------------------------------------------------------------- two CTAs per SM
+// The shared-memory variant again, sized so that TWO CTAs fit on an SM (16-wide k blocks, three stages
+// of 32.5 KB, 2 x 128 TMEM columns, 288 threads): while one CTA runs its epilogue, or waits for its
+// first loads, the other one keeps the tensor pipe busy. With one CTA per SM nothing overlaps a
+// tile's prologue and epilogue, which costs a fifth of the time of a K = 512 product and most of the
+// time of the K = 64 attention products.
+constexpr int BK2 = 16, ST2 = 3, MMA_WARP2 = 8, THREADS2 = 288;
+__host__ __device__ constexpr uint32_t lbo2_bytes(int rows) { return (uint32_t)rows * 16u + 32u; }   // +32: 4 k-chunks x 2 rows per quarter warp
+__host__ __device__ constexpr uint32_t tile2_bytes(int rows) { return (BK2 / 4) * lbo2_bytes(rows); }
+__host__ __device__ constexpr uint32_t stage2_bytes(int bn) { return 2 * tile2_bytes(BM) + 2 * tile2_bytes(bn); }
+__host__ __device__ constexpr uint32_t smem2_bytes(int bn) {
+    return (ST2 * stage2_bytes(bn) > 8u * 32u * 33u * 4u ? ST2 * stage2_bytes(bn) : 8u * 32u * 33u * 4u) + 256;
+}
+
+template <bool KC, int ROWS>
+struct TileMap2 {                                   // ROWS x 16 values = ROWS / 64 chunks of 4 per thread
+    __device__ __forceinline__ static void at(int t, int p, int &row, int &kc) {
+        if (KC) { kc = t % 4; row = t / 4 + 64 * p; }
+        else { row = t % ROWS; kc = t / ROWS + (CONV_THREADS / ROWS) * p; }
+    }
+};
+
+template <class F, bool AK, bool BKC, int BN, int SPLIT>
+__device__ __forceinline__ void gemm_tc2_tile(const F &f, float *__restrict__ partial, uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int M = F::M, N = F::N, K = F::K;
+    constexpr int TILES_N = (N + BN - 1) / BN;
+    constexpr uint32_t LBO_A = lbo2_bytes(BM), LBO_B = lbo2_bytes(BN);
+    constexpr uint32_t TA = tile2_bytes(BM), TB = tile2_bytes(BN), STAGE = stage2_bytes(BN);
+    constexpr uint32_t BAR_OFF = smem2_bytes(BN) - 256;
+    constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK2 - 1) / BK2 * BK2;
+    constexpr int PA = BM / 64, PB = BN / 64;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int tile_m = blockIdx.x / TILES_N, tile_n = blockIdx.x % TILES_N;
+    const int bt = SPLIT > 1 ? blockIdx.y / SPLIT : blockIdx.y;
+    const int sp = SPLIT > 1 ? blockIdx.y % SPLIT : 0;
+    const int m0 = tile_m * BM, n0 = tile_n * BN;
+    const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
+    const int nkb = k_end > k_begin ? (k_end - k_begin + BK2 - 1) / BK2 : 0;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFF);                // full[3], empty[3], accum
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + BAR_OFF + 64);
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + BAR_OFF + 72);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (ST2 + s); };
+    const uint32_t accum = bar0 + 8u * (2 * ST2);
+
+    if (t == 0) {
+        for (int s = 0; s < ST2; s++) { mbar_init(full(s), CONV_THREADS); mbar_init(empty(s), 1); }
+        mbar_init(accum, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < MMA_WARP2) {
+        // ---------------------------------------------------------------- converters (one group, prefetch one block ahead)
+        float va[PA][4], vb[PB][4];
+        auto fetch = [&](int k0) {
+#pragma unroll
+            for (int p = 0; p < PA; p++) {
+                int row, kc;
+                TileMap2<AK, BM>::at(t, p, row, kc);
+                const int m = m0 + row, k = k0 + kc * 4;
+                if (m < M && k < k_end) f.a4(m, k, bt, va[p]);
+                else { va[p][0] = va[p][1] = va[p][2] = va[p][3] = 0.0f; }
+            }
+#pragma unroll
+            for (int p = 0; p < PB; p++) {
+                int row, kc;
+                TileMap2<BKC, BN>::at(t, p, row, kc);
+                const int n = n0 + row, k = k0 + kc * 4;
+                if (n < N && k < k_end) f.b4(k, n, bt, vb[p]);
+                else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+            }
+        };
+        if (nkb > 0) fetch(k_begin);
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % ST2;
+            const uint32_t ph = (kb / ST2) & 1;
+            if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
+            uint8_t *st = smem + s * STAGE;
+#pragma unroll
+            for (int p = 0; p < PA; p++) {
+                int row, kc;
+                TileMap2<AK, BM>::at(t, p, row, kc);
+                split_store(st, st + TA, kc * LBO_A + row * 16, va[p]);
+            }
+#pragma unroll
+            for (int p = 0; p < PB; p++) {
+                int row, kc;
+                TileMap2<BKC, BN>::at(t, p, row, kc);
+                split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
+            }
+            if (kb + 1 < nkb) fetch(k_begin + (kb + 1) * BK2);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(full(s));
+        }
+    } else if (lane == 0) {
+        // ---------------------------------------------------------------- MMA issuer
+        constexpr uint32_t IDESC = instr_desc(BM, BN);
+        const uint32_t base = smem_u32(smem);
+        for (int kb = 0; kb < nkb; kb++) {
+            const int s = kb % ST2;
+            const uint32_t ph = (kb / ST2) & 1;
+            if (!mbar_wait(full(s), ph)) { *failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
+#pragma unroll
+            for (int j = 0; j < BK2 / 8; j++) {
+                const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_A, LBO_A), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
+                const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
+                mma_tf32(tmem + BN, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
+                mma_tf32(tmem + BN, dal, dbh, IDESC, 1u);
+                mma_tf32(tmem, dah, dbh, IDESC, (kb | j) ? 1u : 0u);
+            }
+            mma_commit(empty(s));
+        }
+        mma_commit(accum);
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    if (warp < MMA_WARP2) {
+        const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
+        if (!ok) *failed = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);
+        const int q = warp & 3;
+        constexpr int CHUNKS = BN / 32;
+        for (int c = warp >> 2; c < CHUNKS; c += MMA_WARP2 / 4) {
+            uint32_t r[32], r2[32];
+            if (ok && nkb > 0) {
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(BN + 32 * c), r2);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = r2[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
+            __syncwarp();
+            const int n = n0 + 32 * c + lane;
+            for (int rr = 0; rr < 32; rr++) {
+                const int m = m0 + 32 * q + rr;
+                const float v = stage_f[rr * 33 + lane];
+                if (m < M && n < N) {
+                    if (SPLIT > 1) partial[(((long)bt * SPLIT + sp) * M + m) * N + n] = v;
+                    else f.epi(m, n, bt, v * F::ALPHA);
+                }
+            }
+            __syncwarp();
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == MMA_WARP2) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
+    }
+    if (t == 0 && *failed) atomicExch(status, TIMEOUT);
+}
+
+
+// ---------------------------------------------------------------------------- CTA pairs (cta_group::2)
+// A 128 x 128 x 8 kind::tf32 MMA takes ~39 ns and reads 8 KB of shared memory: with the converters'
+// own stores a single CTA asks its shared memory for more than 128 B/clk, and the tensor pipe idles
+// half of the time. Two CTAs of a cluster therefore share one 256 x BN tile: CTA r converts A rows
+// 128 r .. 128 r + 127 and B rows (n) r BN/2 .. r BN/2 + BN/2 - 1 into its own shared memory, and ONE thread of
+// CTA 0 issues tcgen05.mma.cta_group::2 (M = 256, N = BN): both tensor cores run, each reads its
+// own A and both halves of B, and each keeps its 128 accumulator rows in its own TMEM. Per flop
+// the shared-memory traffic is half that of the single-CTA tile.
+//   full[s]   lives in CTA 0; one arrival per converter warp of BOTH CTAs (the peer's arrive through
+//             the cluster window, release.cluster after the generic->async proxy fence)
+//   empty[s], accum: one copy per CTA, flipped by tcgen05.commit.cta_group::2 multicast to both.
+// Each CTA allocates its tensor memory itself (cta_group::1, same column count, one CTA per SM, so
+// both get the same base; the kernel checks that and reports TIMEOUT status if not).
+// Every mbarrier wait is clock-bounded as above; the two cluster barriers are reached by all
+// threads because no loop before them is unbounded.
+__host__ __device__ constexpr uint32_t pair_stage_bytes(int bn) { return 2 * tile_bytes(BM) + 2 * tile_bytes(bn / 2); }
+__host__ __device__ constexpr uint32_t pair_smem_bytes(int bn) {
+    return (STAGES * pair_stage_bytes(bn) > 116u * 1024u ? STAGES * pair_stage_bytes(bn) : 116u * 1024u) + 256;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (true) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > (1LL << 31)) return false;
+    }
+}
+__device__ __forceinline__ void mma_tf32_pair(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier at this shared-memory offset in both CTAs of the pair once all MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+
+// Launched with cluster dimensions (2, 1, 1): blockIdx.x >> 1 is the tile, %cluster_ctarank the half.
+template <class F, bool AK, bool BKC, int BN, int SPLIT>
+__device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict__ partial, uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int M = F::M, N = F::N, K = F::K;
+    constexpr int BH = BN / 2;                                                   // B rows converted by one CTA
+    constexpr int TILES_N = (N + BN - 1) / BN;
+    constexpr uint32_t LBO_A = lbo_bytes(BM), LBO_B = lbo_bytes(BH);
+    constexpr uint32_t TA = tile_bytes(BM), TB = tile_bytes(BH), STAGE = pair_stage_bytes(BN);
+    constexpr uint32_t BAR_OFF = pair_smem_bytes(BN) - 256;
+    constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK - 1) / BK * BK;
+    constexpr int NST = STAGES;
+    constexpr uint32_t FULL_ARRIVALS = 2 * (CONV_THREADS / 32);
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cid = blockIdx.x >> 1;
+    const int tile_m = cid / TILES_N, tile_n = cid % TILES_N;
+    const int bt = SPLIT > 1 ? blockIdx.y / SPLIT : blockIdx.y;
+    const int sp = SPLIT > 1 ? blockIdx.y % SPLIT : 0;
+    const int m0 = tile_m * (2 * BM) + (int)rank * BM;                           // this CTA's accumulator rows
+    const int n0 = tile_n * BN;
+    const int nb0 = n0 + (int)rank * BH;                                         // this CTA's B rows
+    const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
+    const int nkb = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFF);               // full[3], empty[3], accum
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + BAR_OFF + 64);
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + BAR_OFF + 72);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (NST + s); };
+    const uint32_t accum = bar0 + 8u * (2 * NST);
+
+    if (t == 0) {
+        for (int s = 0; s < NST; s++) { mbar_init(full(s), FULL_ARRIVALS); mbar_init(empty(s), 1); }
+        mbar_init(accum, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();                                                              // both CTAs' barriers and TMEM exist
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < MMA_WARP) {
+        // ---------------------------------------------------------------- converters
+        const int grp = warp >> 3;
+        const int tc = threadIdx.x & (CONV_THREADS - 1);
+        float va[BM / 32][4], vb[BH / 32][4];
+        auto fetch = [&](int k0) {
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(tc, p, row, kc);
+                const int m = m0 + row, k = k0 + kc * 4;
+                if (m < M && k < k_end) f.a4(m, k, bt, va[p]);
+                else { va[p][0] = va[p][1] = va[p][2] = va[p][3] = 0.0f; }
+            }
+#pragma unroll
+            for (int p = 0; p < BH / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BH>::at(tc, p, row, kc);
+                const int n = nb0 + row, k = k0 + kc * 4;
+                if (n < N && k < k_end) f.b4(k, n, bt, vb[p]);
+                else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+            }
+        };
+        const uint32_t full_leader0 = map_to_cta(full(0), 0);
+        if (grp < nkb) fetch(k_begin + grp * BK);
+        for (int kb = grp; kb < nkb; kb += CONV_GROUPS) {
+            const int s = kb % NST;
+            const uint32_t ph = (kb / NST) & 1;
+            if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
+            uint8_t *st = smem + s * STAGE;
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(tc, p, row, kc);
+                split_store(st, st + TA, kc * LBO_A + row * 16, va[p]);
+            }
+#pragma unroll
+            for (int p = 0; p < BH / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BH>::at(tc, p, row, kc);
+                split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
+            }
+            if (kb + CONV_GROUPS < nkb) fetch(k_begin + (kb + CONV_GROUPS) * BK);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(full_leader0 + 8u * s);
+        }
+    } else if (lane == 0 && rank == 0) {
+        // ---------------------------------------------------------------- MMA issuer (CTA 0 of the pair only)
+        constexpr uint32_t IDESC = instr_desc(2 * BM, BN);
+        const uint32_t base = smem_u32(smem);
+        uint32_t peer_tmem;
+        asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(peer_tmem) : "r"(map_to_cta(smem_u32(tmem_slot), 1)) : "memory");
+        if (peer_tmem != tmem) *failed = 1;
+        for (int kb = 0; kb < nkb && !*failed; kb++) {
+            const int s = kb % NST;
+            const uint32_t ph = (kb / NST) & 1;
+            if (!mbar_wait_cluster(full(s), ph)) { *failed = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
+#pragma unroll
+            for (int j = 0; j < BK / 8; j++) {
+                const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_A, LBO_A), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
+                const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
+                mma_tf32_pair(tmem + BN, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
+                mma_tf32_pair(tmem + BN, dal, dbh, IDESC, 1u);
+                mma_tf32_pair(tmem, dah, dbh, IDESC, (kb | j) ? 1u : 0u);
+            }
+            mma_commit_pair(empty(s));
+        }
+        mma_commit_pair(accum);
+    }
+
+    // ---------------------------------------------------------------- epilogue: 128 rows x BN columns per CTA
+    if (warp < MMA_WARP) {
+        const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
+        if (!ok) *failed = 1;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);
+        const int q = warp & 3;
+        constexpr int CHUNKS = BN / 32;
+        for (int c = warp >> 2; c < CHUNKS; c += MMA_WARP / 4) {
+            uint32_t r[32], r2[32];
+            if (ok && nkb > 0) {
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(32 * c), r);
+                tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(BN + 32 * c), r2);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = r2[i] = 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
+            __syncwarp();
+            const int n = n0 + 32 * c + lane;
+            for (int rr = 0; rr < 32; rr++) {
+                const int m = m0 + 32 * q + rr;
+                const float v = stage_f[rr * 33 + lane];
+                if (m < M && n < N) {
+                    if (SPLIT > 1) partial[(((long)bt * SPLIT + sp) * M + m) * N + n] = v;
+                    else f.epi(m, n, bt, v * F::ALPHA);
+                }
+            }
+            __syncwarp();
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();                                                              // nobody leaves while the peer may still touch this CTA's shared memory
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
+    }
+    if (t == 0 && *failed) atomicExch(status, TIMEOUT);
+}
+
 }  // namespace tc
 }  // namespace anvil

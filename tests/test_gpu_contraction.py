@@ -23,15 +23,18 @@ CASES = [
     (256, 64, 256, 6, False, False, False, False, 0.125, False, False),      # batched, 64-wide tile
     (256, 256, 64, 4, False, True, False, False, 1.0, False, False),
     (130, 70, 36, 2, True, True, True, False, 1.0, False, False),
+    (300, 300, 72, 2, True, False, True, False, 1.0, False, False),           # ragged in every direction, two tile columns
     (1024, 1024, 1024, 1, False, False, True, False, 1.0, False, False),
     (16384, 512, 2048, 1, False, False, True, False, 1.0, False, False),       # a transformer MLP product (A is 134 MB)
 ]
 
 
 def run_case(case, tc):
-    """tc: True / "ts" (A tiles in tensor memory), "ss" (both operands in shared memory), False (CUDA cores)."""
+    """tc: True (the emitter's choice), "pair" (two CTAs of a cluster on one 256-row tile, cta_group::2; shapes too
+    small for it take the emitter's choice), "ts" (A tiles in tensor memory), "ss" (operands in shared memory, two CTAs
+    per SM), "ss32" (operands in shared memory, one CTA per SM, 32-wide k blocks), False (CUDA cores)."""
     M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out = case
-    os.environ["ANVIL_B200_TC"] = {True: "1", "ts": "ts", "ss": "ss", False: "0"}[tc]
+    os.environ["ANVIL_B200_TC"] = {True: "1", False: "0"}.get(tc, tc)
     try:
         prog, kern, A, B, C, bias_b = contraction_program(M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out)
         dp = DeviceProgram(prog, graphs=False)
@@ -53,7 +56,7 @@ def run_case(case, tc):
     return err, note
 
 
-@pytest.mark.parametrize("variant", ["ts", "ss"])
+@pytest.mark.parametrize("variant", ["pair", "ts", "ss", "ss32"])
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[:4])))
 def test_tensor_core_contraction(case, variant):
     err, note = run_case(case, tc=variant)
