@@ -89,6 +89,7 @@ class Scope:
         self.lets: dict = {}            # let id -> {lane: code}
         self.acc_name = "acc"           # C identifier that holds the kernel's reduction result
         self.acc_lanes = False          # one result per lane (`acc_0` ...): lanes run along an output var
+        self.preloaded: dict = {}       # (root id, offset key) -> C expression holding that element already
 
     # ---- which nodes vary along the vectorised var
     def off_depends(self, a: kir.Affine) -> bool:
@@ -225,6 +226,10 @@ class Scope:
         raise NotImplementedError(k)
 
     def load(self, e: kir.E, lane) -> str:
+        if self.preloaded:
+            hit = self.preloaded.get((e.buf.root.id, e.off.key()))
+            if hit is not None:
+                return hit
         p = self.kg.ptr(e.buf, False)
         if self.lanes % 4 == 0 and self.lanes >= 4 and self.depends(e) and an.stride_of(e.off, self.vv) == 1 \
                 and an.aligned4(e.off, self.vv):
@@ -328,7 +333,10 @@ class Scope:
             return
         for lane in range(L):
             target = f"{p}[{self.affine(st.offset, lane)}]"
-            if st.accumulate:
+            old = self.preloaded.get((st.buf.root.id, st.offset.key())) if st.accumulate else None
+            if old is not None:
+                self.emit(f"{target} = ({old}) + ({vals[lane]});")
+            elif st.accumulate:
                 if exclusive or not self.kg.parallel:
                     self.emit(f"{target} += {vals[lane]};")
                 else:
@@ -815,6 +823,56 @@ class KernelGen:
             sc.statements()
             return None
         fe = self.functor_method("void epi(int m, int n, int bt, float acc)", dm + dn + db, epi)
+
+        def touch(sc):
+            # L2 prefetch of what the statements read at element (m, n): residuals, `+=` targets. The
+            # resident tensor-core template issues it one tile ahead of the epilogue that needs it.
+            seen = set()
+            reads = [(n.buf, n.off) for st in k.stmts for n in st.value.walk() if n.k == "load"]
+            reads += [(st.buf, st.offset) for st in k.stmts if isinstance(st, kir.Store) and st.accumulate]
+            for buf, off in reads:
+                if not off.is_plain() or off.scalars() or (buf.root.id, off.key()) in seen:
+                    continue
+                vs = off.vars()
+                if not (any(v in vs for v in c.mvars) and any(v in vs for v in c.nvars)):
+                    continue                                 # a bias row or a per-row scalar: cached anyway
+                seen.add((buf.root.id, off.key()))
+                sc.emit(f"anvil::prefetch_l2({self.ptr(buf, False)} + ({sc.affine(off, 0)}));")
+            return None
+        fe = fe + self.functor_method("void epi_touch(int m, int n, int bt)", dm + dn + db, touch)
+
+        # Two-phase form of the statements: epi_loads fetches what they read at (m, n) — tensors this kernel
+        # never writes, and the old value of an exclusive `+=` — and epi2 runs them on those values, so a
+        # caller can issue the loads of several rows before the first store.
+        written = {st.buf.root.id for st in k.stmts if isinstance(st, kir.Store)}
+        pre: list = []
+        for st in k.stmts:
+            cands = [(n.buf, n.off, False) for n in st.value.walk() if n.k == "load" and n.dt == F32]
+            if isinstance(st, kir.Store) and st.accumulate and st.buf.dtype == F32 and an.exclusive_store(k, st) \
+                    and sum(1 for x in k.stmts if isinstance(x, kir.Store) and x.buf.root.id == st.buf.root.id) == 1:
+                cands.append((st.buf, st.offset, True))
+            for buf, off, own in cands:
+                vs = off.vars()
+                if not off.is_plain() or not (any(v in vs for v in c.mvars) and any(v in vs for v in c.nvars)):
+                    continue
+                if (buf.root.id in written) != own or any(b.root.id == buf.root.id and o.key() == off.key() for b, o, _ in pre):
+                    continue
+                if len(pre) < 4:
+                    pre.append((buf, off, own))
+        nld = len(pre)
+
+        def loads(sc):
+            for i, (buf, off, _) in enumerate(pre):
+                sc.emit(f"ld[{i}] = {self.ptr(buf, False)}[{sc.affine(off, 0)}];")
+            return None
+
+        def epi2(sc):
+            sc.preloaded = {(buf.root.id, off.key()): f"ld[{i}]" for i, (buf, off, _) in enumerate(pre)}
+            sc.statements()
+            return None
+        fe = fe + [f"    static constexpr int NLD = {nld};"]
+        fe = fe + self.functor_method(f"void epi_loads(int m, int n, int bt, float (&ld)[{max(nld, 1)}])", dm + dn + db, loads)
+        fe = fe + self.functor_method(f"void epi2(int m, int n, int bt, float acc, const float (&ld)[{max(nld, 1)}])", dm + dn + db, epi2)
         tiles = ((M + 127) // 128) * ((N + 127) // 128)
         S = 1
         if tiles * NB < 148 and K >= 256:
@@ -873,9 +931,10 @@ class KernelGen:
         fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
         fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
         variant = tc_variant(c.a_kcontig, M, N, K)
-        pair = variant == "pair"
+        pp = variant == "pp"
+        pair = variant == "pair" or pp
         if pair:                                 # 256 x BN tile per cluster of two CTAs
-            BN = 256 if N >= 256 else 128
+            BN = 256 if N >= 256 or pp else 128
             tiles = ((M + 255) // 256) * ((N + BN - 1) // BN)
             slots = 74
         else:
@@ -895,8 +954,18 @@ class KernelGen:
         # A in tensor memory pays off when A is read along m (lane = row gives coalesced loads); a
         # k-contiguous A is read faster by the shared-memory variant's 8-lanes-per-row mapping
         ts = variant == "ts"
+        tile_tail = ">"
         attrs = ""
-        if pair:
+        grid_x = 2 * tiles if pair else tiles
+        grid_y = NB * S
+        if pp:                                   # resident clusters walk over (tile, batch, split) items
+            accs = 1 if (K + S - 1) // S <= 512 else 2
+            smem, threads, per_sm = "anvil::tc::pp_smem_bytes()", "anvil::tc::PP_THREADS", 1
+            tile_fn = f"anvil::tc::gemm_tc_pair_persistent<{fn}, {AK}, {BKC}, "
+            tile_tail = f", {accs}>"
+            attrs = "__cluster_dims__(2, 1, 1) "
+            grid_x, grid_y = 2 * min(tiles * NB * S, 74), 1
+        elif pair:
             smem, threads, per_sm = f"anvil::tc::pair_smem_bytes({BN})", "anvil::tc::THREADS", 1
             tile_fn = f"anvil::tc::gemm_tc_pair_tile<{fn}, {AK}, {BKC}, {BN}, "
             attrs = "__cluster_dims__(2, 1, 1) "
@@ -914,22 +983,22 @@ class KernelGen:
         if S == 1:
             kname = base
             src += [f"__global__ void {attrs}__launch_bounds__({threads}, {per_sm}) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
-                    f"    {tile_fn}1>({fn}{{A}}, nullptr, {status});", "}"]
+                    f"    {tile_fn}1{tile_tail}({fn}{{A}}, nullptr, {status});", "}"]
         else:
             kname = base + "_part"
             self.gen.need_scratch(4 * M * N * NB * S)
             soff = self.gen.plan.scratch_off
             src += [f"__global__ void {attrs}__launch_bounds__({threads}, {per_sm}) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
-                    f"    {tile_fn}{S}>({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
+                    f"    {tile_fn}{S}{tile_tail}({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
         launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
                       f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
-        launch.append(f"{kname}<<<dim3({2 * tiles if pair else tiles}, {NB * S}), {threads}, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        launch.append(f"{kname}<<<dim3({grid_x}, {grid_y}), {threads}, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
         if S > 1:
             fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
             launch.append(self.launch_line(base, fb_, 256))
-        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}" + (" A-tmem" if ts else " pair" if pair else "")
+        self.notes = f"gemm tc {NB}x{M}x{N}x{K} S{S}" + (" A-tmem" if ts else " pp" if pp else " pair" if pair else "")
         self.contraction = c
         return "\n".join(src), launch
 
@@ -950,21 +1019,24 @@ def use_tensor_cores() -> bool:
 
 
 def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
-    """Which tcgen05 template a contraction takes (ANVIL_B200_TC=pair|ss|ss32|ts forces one where it applies):
-    "pair" two CTAs of a cluster share a 256 x 256 (or 256 x 128) tile, tcgen05.mma.cta_group::2 — needs
-           M >= 256 and N >= 128;
-    "ts"   A tiles in tensor memory — when A is read along m (measured 148-151 vs 124-130 TFLOP/s);
-    "ss"   operands in shared memory, 16-wide k blocks, two CTAs per SM — short reductions (K <= 128),
-           where a tile is mostly prologue and epilogue (QK^T-type products: 88 vs 73 TFLOP/s);
-    "ss32" operands in shared memory, 32-wide k blocks, one CTA per SM — everything else
-           (K = 2048: 134 vs 117 TFLOP/s for "ss")."""
+    """Which tcgen05 template a contraction takes (ANVIL_B200_TC=pp|pair|ss|ss32|ts forces one where it applies):
+    "pp"   resident clusters of two CTAs on 256 x 256 tiles (tcgen05.mma.cta_group::2), converter / MMA /
+           epilogue warps overlapping across tiles — needs M >= 256 and N >= 128; the default there
+           (16384x2048x512: 232-245 TFLOP/s against 150-154 for "ss32");
+    "pair" the same tile, one launch-time CTA pair per tile (kept for comparison);
+    "ts"   A tiles in tensor memory — when A is read along m and the output is small or narrow;
+    "ss"   operands in shared memory, 16-wide k blocks, two CTAs per SM — short reductions (K <= 128)
+           on narrow outputs;
+    "ss32" operands in shared memory, 32-wide k blocks, one CTA per SM — the remaining shapes."""
     import os
     v = os.environ.get("ANVIL_B200_TC", "1")
     pair_ok = M >= 256 and N >= 128
-    if v == "pair" and not pair_ok:
+    if v in ("pair", "pp") and not pair_ok:
         v = "1"
-    if v in ("pair", "ss", "ts", "ss32"):
+    if v in ("pair", "pp", "ss", "ts", "ss32"):
         return v
+    if pair_ok and (a_kcontig or M * N > 512 * 512):
+        return "pp"
     if not a_kcontig:
         return "ts"
     return "ss" if K <= 128 else "ss32"

@@ -30,6 +30,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Optional phase stamps for timing studies: a translation unit may define ANVIL_TC_TRACE(slot) before
+// including this header; by default it expands to nothing.
+#ifndef ANVIL_TC_TRACE
+#define ANVIL_TC_TRACE(slot)
+#endif
+
 namespace anvil {
 namespace tc {
 
@@ -251,6 +257,7 @@ __device__ __forceinline__ void gemm_tc_tile(const F &f, float *__restrict__ par
             for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
             __syncwarp();
             const int n = n0 + 32 * c + lane;
+#pragma unroll 4
             for (int rr = 0; rr < 32; rr++) {
                 const int m = m0 + 32 * q + rr;
                 const float v = stage_f[rr * 33 + lane];
@@ -439,6 +446,7 @@ __device__ __forceinline__ void gemm_tc_ts_tile(const F &f, float *__restrict__ 
             for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
             __syncwarp();
             const int n = n0 + 32 * c + lane;
+#pragma unroll 4
             for (int rr = 0; rr < 32; rr++) {
                 const int m = m0 + 32 * q + rr;
                 const float v = stage_f[rr * 33 + lane];
@@ -610,6 +618,7 @@ __device__ __forceinline__ void gemm_tc2_tile(const F &f, float *__restrict__ pa
             for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
             __syncwarp();
             const int n = n0 + 32 * c + lane;
+#pragma unroll 4
             for (int rr = 0; rr < 32; rr++) {
                 const int m = m0 + 32 * q + rr;
                 const float v = stage_f[rr * 33 + lane];
@@ -712,6 +721,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
     const int nb0 = n0 + (int)rank * BH;                                         // this CTA's B rows
     const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
     const int nkb = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
+    if (t == 0) { ANVIL_TC_TRACE(0); }
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFF);               // full[3], empty[3], accum
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + BAR_OFF + 64);
@@ -736,6 +746,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
     cluster_sync();                                                              // both CTAs' barriers and TMEM exist
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    if (t == 0) { ANVIL_TC_TRACE(1); }
 
     if (warp < MMA_WARP) {
         // ---------------------------------------------------------------- converters
@@ -795,6 +806,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             const int s = kb % NST;
             const uint32_t ph = (kb / NST) & 1;
             if (!mbar_wait_cluster(full(s), ph)) { *failed = 1; break; }
+            if (kb == 0) { ANVIL_TC_TRACE(2); }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
 #pragma unroll
@@ -808,12 +820,14 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             mma_commit_pair(empty(s));
         }
         mma_commit_pair(accum);
+        ANVIL_TC_TRACE(3);
     }
 
     // ---------------------------------------------------------------- epilogue: 128 rows x BN columns per CTA
     if (warp < MMA_WARP) {
         const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
         if (!ok) *failed = 1;
+        if (t == 0) { ANVIL_TC_TRACE(4); }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);
         const int q = warp & 3;
@@ -831,6 +845,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             for (int i = 0; i < 32; i++) stage_f[lane * 33 + i] = __uint_as_float(r[i]) + __uint_as_float(r2[i]);
             __syncwarp();
             const int n = n0 + 32 * c + lane;
+#pragma unroll 4
             for (int rr = 0; rr < 32; rr++) {
                 const int m = m0 + 32 * q + rr;
                 const float v = stage_f[rr * 33 + lane];
@@ -841,6 +856,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             }
             __syncwarp();
         }
+        if (t == 0) { ANVIL_TC_TRACE(5); }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -849,6 +865,271 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
     }
+    if (t == 0) { ANVIL_TC_TRACE(6); }
+    if (t == 0 && *failed) atomicExch(status, TIMEOUT);
+}
+
+
+// ---------------------------------------------------------------------------- persistent CTA pairs
+// Timeline of one 256 x 256 x 512 tile of the kernel above (globaltimer stamps, B200): 0.9 us set-up,
+// 3.1 us until the first stage is full, 13.1 us main loop (the tensor pipe's own rate), 1.2 us until
+// the accumulator is seen, 3.6 us epilogue (14.8 us when the epilogue reads what it adds to),
+// 0.7 us exit — the tensor pipe works during 58 % of a tile's life. Here one cluster per SM pair stays
+// resident and walks over the work items (tile, batch, k split) in a fixed round-robin order, with
+// the three jobs on different warps so that they overlap across tiles:
+//   warps 0-15  converters, two groups of eight, stage ring and block counter running on across tiles
+//               (the next tile's first stages are filled while the current one is still being stored);
+//   warps 16-23 epilogue: (TMEM lane quarter, column half) each, transposes in their own shared memory;
+//   warp 24     MMA issuer (CTA 0) as above.
+// ACCS = 2 keeps the correction accumulator (one TMEM buffer of 512 columns: the next tile's MMAs wait
+// for the epilogue's loads, the converters do not). ACCS = 1 adds all three products into one accumulator,
+// which costs three roundings toward zero per k-step instead of one (relative error ~7e-9 per unit of
+// chain length) and is used for chains of at most 512; the 512 columns then hold two buffers and
+// the epilogue of a tile runs under the main loop of the next.
+//   tfull[b]  per CTA, flipped by the multicast commit after a tile's last MMA
+//   tempty[b] in CTA 0, one arrival per epilogue warp of both CTAs once its tcgen05.ld are done.
+constexpr int PP_CONV_GROUPS = 2, PP_EPI_WARPS = 8;
+constexpr int PP_MMA_WARP = 8 * PP_CONV_GROUPS + PP_EPI_WARPS, PP_THREADS = 32 * PP_MMA_WARP + 32;
+constexpr int PP_SLOTS = 74;                                      // clusters resident at once: one per SM pair
+__host__ __device__ constexpr uint32_t pp_smem_bytes() {
+    return STAGES * pair_stage_bytes(256) + PP_EPI_WARPS * 32 * 33 * 4 + 256;
+}
+
+template <class F, bool AK, bool BKC, int SPLIT, int ACCS>
+__device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__restrict__ partial, uint32_t *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int M = F::M, N = F::N, K = F::K;
+    constexpr int BN = 256, BH = 128;
+    constexpr int TILES_N = (N + BN - 1) / BN, TILES = ((M + 2 * BM - 1) / (2 * BM)) * TILES_N;
+    constexpr int WORK = TILES * F::NB * SPLIT;
+    constexpr int NBUF = ACCS == 1 ? 2 : 1;
+    constexpr uint32_t BUF_COLS = ACCS * BN;
+    constexpr uint32_t LBO_A = lbo_bytes(BM), LBO_B = lbo_bytes(BH);
+    constexpr uint32_t TA = tile_bytes(BM), TB = tile_bytes(BH), STAGE = pair_stage_bytes(BN);
+    constexpr uint32_t EPI_OFF = STAGES * STAGE, BAR_OFF = pp_smem_bytes() - 256;
+    constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK - 1) / BK * BK;
+    constexpr int NST = STAGES, G = PP_CONV_GROUPS;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cid = blockIdx.x >> 1, ncl = gridDim.x >> 1;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFF);               // full[3], empty[3], tfull[2], tempty[2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + BAR_OFF + 96);
+    volatile uint32_t *failed = reinterpret_cast<volatile uint32_t *>(smem + BAR_OFF + 104);
+    const uint32_t bar0 = smem_u32(bars);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (NST + s); };
+    auto tfull = [&](int b) { return bar0 + 8u * (2 * NST + b); };
+    auto tempty = [&](int b) { return bar0 + 8u * (2 * NST + 2 + b); };
+
+    // One work item: which rows / columns / k range. All roles walk the same sequence w = cid, cid + ncl, ...
+    struct Item { int m0, n0, nb0, bt, sp, k_begin, k_end, nkb; };
+    auto item = [&](int w) {
+        Item it;
+        const int tile = w % TILES, y = w / TILES;
+        it.bt = y / SPLIT; it.sp = y % SPLIT;
+        it.m0 = (tile / TILES_N) * (2 * BM) + (int)rank * BM;
+        it.n0 = (tile % TILES_N) * BN;
+        it.nb0 = it.n0 + (int)rank * BH;
+        it.k_begin = it.sp * KCH; it.k_end = min(K, it.k_begin + KCH);
+        it.nkb = max(1, (it.k_end - it.k_begin + BK - 1) / BK);                 // an empty k range still runs one block of zeros
+        return it;
+    };
+
+    if (t == 0) {
+        for (int s = 0; s < NST; s++) { mbar_init(full(s), 2 * 8); mbar_init(empty(s), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull(b), 1); mbar_init(tempty(b), 2 * PP_EPI_WARPS); }
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        ANVIL_TC_TRACE(0);
+    }
+    if (warp == PP_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    if (t == 0) { ANVIL_TC_TRACE(1); }
+
+    if (warp < 8 * G) {
+        // ---------------------------------------------------------------- converters
+        const int grp = warp >> 3;
+        const int tc = t & (CONV_THREADS - 1);
+        float va[BM / 32][4], vb[BH / 32][4];
+        auto fetch = [&](const Item &it, int kb) {
+            const int k0 = it.k_begin + kb * BK;
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(tc, p, row, kc);
+                const int m = it.m0 + row, k = k0 + kc * 4;
+                if (m < M && k < it.k_end) f.a4(m, k, it.bt, va[p]);
+                else { va[p][0] = va[p][1] = va[p][2] = va[p][3] = 0.0f; }
+            }
+#pragma unroll
+            for (int p = 0; p < BH / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BH>::at(tc, p, row, kc);
+                const int n = it.nb0 + row, k = k0 + kc * 4;
+                if (n < N && k < it.k_end) f.b4(k, n, it.bt, vb[p]);
+                else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+            }
+        };
+        // (w, kb) of this group's current block; `advance` moves it G blocks on
+        int w = cid, kb = grp;
+        Item it = item(w < WORK ? w : 0);
+        auto settle = [&]() { while (w < WORK && kb >= it.nkb) { kb -= it.nkb; w += ncl; if (w < WORK) it = item(w); } };
+        settle();
+        const uint32_t full_leader0 = map_to_cta(full(0), 0);
+        if (w < WORK) fetch(it, kb);
+        for (long n = grp; w < WORK; n += G) {
+            const int s = (int)(n % NST);
+            const uint32_t ph = (uint32_t)(n / NST) & 1u;
+            if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
+            uint8_t *st = smem + s * STAGE;
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(tc, p, row, kc);
+                split_store(st, st + TA, kc * LBO_A + row * 16, va[p]);
+            }
+#pragma unroll
+            for (int p = 0; p < BH / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BH>::at(tc, p, row, kc);
+                split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
+            }
+            kb += G;
+            settle();
+            if (w < WORK) fetch(it, kb);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(full_leader0 + 8u * s);
+        }
+    } else if (warp == PP_MMA_WARP) {
+        if (lane == 0 && rank == 0) {
+            // ------------------------------------------------------------ MMA issuer (CTA 0 of the pair only)
+            constexpr uint32_t IDESC = instr_desc(2 * BM, BN);
+            const uint32_t base = smem_u32(smem);
+            uint32_t peer_tmem;
+            asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(peer_tmem) : "r"(map_to_cta(smem_u32(tmem_slot), 1)) : "memory");
+            if (peer_tmem != tmem) *failed = 1;
+            long n = 0;
+            int i = 0;
+            for (int w = cid; w < WORK && !*failed; w += ncl, i++) {
+                const Item it = item(w);
+                const int buf = i % NBUF;
+                if (!mbar_wait_cluster(tempty(buf), (((uint32_t)(i / NBUF)) & 1u) ^ 1u)) { *failed = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + (uint32_t)buf * BUF_COLS;
+                for (int kb = 0; kb < it.nkb; kb++, n++) {
+                    const int s = (int)(n % NST);
+                    if (!mbar_wait_cluster(full(s), (uint32_t)(n / NST) & 1u)) { *failed = 1; break; }
+                    if (n == 0) { ANVIL_TC_TRACE(2); }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
+#pragma unroll
+                    for (int j = 0; j < BK / 8; j++) {
+                        const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_A, LBO_A), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
+                        const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
+                        if (ACCS == 2) {
+                            mma_tf32_pair(acc + BN, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
+                            mma_tf32_pair(acc + BN, dal, dbh, IDESC, 1u);
+                            mma_tf32_pair(acc, dah, dbh, IDESC, (kb | j) ? 1u : 0u);
+                        } else {                                     // small terms first, then the large one
+                            mma_tf32_pair(acc, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
+                            mma_tf32_pair(acc, dal, dbh, IDESC, 1u);
+                            mma_tf32_pair(acc, dah, dbh, IDESC, 1u);
+                        }
+                    }
+                    mma_commit_pair(empty(s));
+                }
+                mma_commit_pair(tfull(buf));
+            }
+            ANVIL_TC_TRACE(3);
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warps
+        const int e = warp - 8 * G, q = warp & 3, half = e >> 2;
+        float *stage_f = reinterpret_cast<float *>(smem + EPI_OFF) + e * (32 * 33);
+        const uint32_t tempty_leader0 = map_to_cta(tempty(0), 0);
+        constexpr int CPW = (BN / 32) / (PP_EPI_WARPS / 4);                       // column chunks per warp
+        // What the statements read besides the accumulator (a residual, the old value of a `+=`) is
+        // asked into L2 one item ahead: lane = row, one 128-byte line per column chunk.
+        auto touch = [&](const Item &it) {
+            if (SPLIT > 1) return;
+            const int m = it.m0 + 32 * q + lane;
+#pragma unroll
+            for (int cc = 0; cc < CPW; cc++) {
+                const int n = it.n0 + 32 * (half * CPW + cc);
+                if (m < M && n < N) f.epi_touch(m, n, it.bt);
+            }
+        };
+        if (cid < WORK) touch(item(cid));
+        int i = 0;
+        for (int w = cid; w < WORK; w += ncl, i++) {
+            const Item it = item(w);
+            const int buf = i % NBUF;
+            const bool ok = !*failed && mbar_wait(tfull(buf), ((uint32_t)(i / NBUF)) & 1u);
+            if (!ok) { *failed = 1; break; }
+            if (w + ncl < WORK) touch(item(w + ncl));
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + (uint32_t)buf * BUF_COLS + ((uint32_t)(32 * q) << 16);
+            for (int cc = 0; cc < CPW; cc++) {
+                const int c = half * CPW + cc;
+                uint32_t r[32];
+                tmem_ld32(acc + (uint32_t)(32 * c), r);
+                if (ACCS == 2) {
+                    uint32_t r2[32];
+                    tmem_ld32(acc + (uint32_t)(BN + 32 * c), r2);
+#pragma unroll
+                    for (int x = 0; x < 32; x++) r[x] = __float_as_uint(__uint_as_float(r[x]) + __uint_as_float(r2[x]));
+                }
+                if (cc == CPW - 1) {                             // this warp's part of the buffer is in registers: hand it back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8u * buf);
+                }
+#pragma unroll
+                for (int x = 0; x < 32; x++) stage_f[lane * 33 + x] = __uint_as_float(r[x]);
+                __syncwarp();
+                const int n = it.n0 + 32 * c + lane;
+                // eight rows at a time: first everything the statements read, then the statements
+                constexpr int RB = 8, NLD = F::NLD > 0 ? F::NLD : 1;
+                for (int r0 = 0; r0 < 32; r0 += RB) {
+                    const int mb = it.m0 + 32 * q + r0;
+                    float ld[RB][NLD];
+                    if (SPLIT == 1 && F::NLD > 0) {
+#pragma unroll
+                        for (int rr = 0; rr < RB; rr++)
+                            if (mb + rr < M && n < N) f.epi_loads(mb + rr, n, it.bt, ld[rr]);
+                    }
+#pragma unroll
+                    for (int rr = 0; rr < RB; rr++) {
+                        const int m = mb + rr;
+                        const float v = stage_f[(r0 + rr) * 33 + lane];
+                        if (m < M && n < N) {
+                            if (SPLIT > 1) partial[(((long)it.bt * SPLIT + it.sp) * M + m) * N + n] = v;
+                            else f.epi2(m, n, it.bt, v * F::ALPHA, ld[rr]);
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        if (e == 0 && lane == 0) { ANVIL_TC_TRACE(5); }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync();
+    if (warp == PP_MMA_WARP) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    if (t == 0) { ANVIL_TC_TRACE(6); }
     if (t == 0 && *failed) atomicExch(status, TIMEOUT);
 }
 

@@ -30,7 +30,7 @@ CASES = [
 
 
 def run_case(case, tc):
-    """tc: True (the emitter's choice), "pair" (two CTAs of a cluster on one 256-row tile, cta_group::2; shapes too
+    """tc: True (the emitter's choice), "pp" (resident CTA pairs walking over the tiles), "pair" (two CTAs of a cluster on one 256-row tile, cta_group::2; shapes too
     small for it take the emitter's choice), "ts" (A tiles in tensor memory), "ss" (operands in shared memory, two CTAs
     per SM), "ss32" (operands in shared memory, one CTA per SM, 32-wide k blocks), False (CUDA cores)."""
     M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out = case
@@ -56,7 +56,7 @@ def run_case(case, tc):
     return err, note
 
 
-@pytest.mark.parametrize("variant", ["pair", "ts", "ss", "ss32"])
+@pytest.mark.parametrize("variant", ["pp", "pair", "ts", "ss", "ss32"])
 @pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[:4])))
 def test_tensor_core_contraction(case, variant):
     err, note = run_case(case, tc=variant)
