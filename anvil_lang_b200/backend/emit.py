@@ -638,6 +638,7 @@ class KernelGen:
         lines += self.decode("u", k.domain, self.names, ind)
         lines.append(f"{ind}{T} acc = {OP}::id<{T}>();")
         lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RNL}L, rbeg + {chunk}L);")
+        lines.append("#pragma unroll 4")                 # several rows' loads in flight; the adds keep their order
         lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
         inner = ind + "    "
         lines.append(f"{inner}const {index_t(RNL)} rr = ({index_t(RNL)})rr_;")
@@ -688,7 +689,7 @@ class KernelGen:
         # split: partial results to scratch, second kernel combines them in order and runs the statements
         self.gen.need_scratch(4 * ON * S)
         soff = self.gen.plan.scratch_off
-        lines.append(f"{ind}if (ry == 0 && live) (({T} *)(A + {soff}UL))[o_ * {S} + blockIdx.y] = acc;")
+        lines.append(f"{ind}if (ry == 0 && live) (({T} *)(A + {soff}UL))[blockIdx.y * {ON}L + o_] = acc;")   # [slice][output]
         part = [self.comment(f"split reduction, part 1 of 2 ({layout}, {S} CTAs per output group)"),
                 self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
         # final
@@ -700,7 +701,8 @@ class KernelGen:
               f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
         fl += self.decode("u", k.domain, self.names, "        ")
         fl.append(f"        {T} acc = {OP}::id<{T}>();")
-        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const {T} *)(A + {soff}UL))[tid * {S} + p]);")
+        fl.append("#pragma unroll 8")                    # slices are added in index order; the loads run ahead
+        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const {T} *)(A + {soff}UL))[p * {ON}L + tid]);")
         final = [self.comment("split reduction, part 2 of 2"), self.head(base, THREADS)] + self.pointer_decls() \
             + fl + fsc.lines + ["    }", "}"]
         self.ptrs = {**saved, **self.ptrs}
@@ -730,6 +732,7 @@ class KernelGen:
         lines += self.decode("u", k.domain, self.names, ind, vv, 4) + self.lane_vars(vv, 4, ind)
         lines.append(f"{ind}float acc_0 = {OP}::id<float>(), acc_1 = acc_0, acc_2 = acc_0, acc_3 = acc_0;")
         lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RN}L, rbeg + {chunk}L);")
+        lines.append("#pragma unroll 4")                 # several rows' loads in flight; the adds keep their order
         lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
         inner = ind + "    "
         lines.append(f"{inner}const {index_t(RN)} rr = ({index_t(RN)})rr_;")
@@ -771,7 +774,7 @@ class KernelGen:
         soff = self.gen.plan.scratch_off
         lines.append(f"{ind}if (ry == 0 && live) {{")
         for i in range(4):
-            lines.append(f"{ind}    ((float *)(A + {soff}UL))[(o_ * 4 + {i}) * {S} + blockIdx.y] = acc_{i};")
+            lines.append(f"{ind}    ((float *)(A + {soff}UL))[blockIdx.y * {ON}L + o_ * 4 + {i}] = acc_{i};")
         lines.append(f"{ind}}}")
         part = [self.comment(f"split reduction, part 1 of 2 (col, 4 outputs per thread, {S} CTAs per output group)"),
                 self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
@@ -783,7 +786,8 @@ class KernelGen:
               f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
         fl += self.decode("u", k.domain, self.names, "        ")
         fl.append(f"        float acc = {OP}::id<float>();")
-        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const float *)(A + {soff}UL))[tid * {S} + p]);")
+        fl.append("#pragma unroll 8")
+        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const float *)(A + {soff}UL))[p * {ON}L + tid]);")
         final = [self.comment("split reduction, part 2 of 2"), self.head(base, THREADS)] + self.pointer_decls() \
             + fl + fsc.lines + ["    }", "}"]
         self.ptrs = {**saved, **self.ptrs}
@@ -931,6 +935,20 @@ class KernelGen:
         fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
         fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
         variant = tc_variant(c.a_kcontig, M, N, K)
+        if variant == "pp":                      # L2 prefetch of the operand element (m, k) / (k, n): issued some blocks ahead
+            dks = self.decode("(uint32_t)k", c.kvars, self.names, ind)
+
+            def operand_touch(operand):
+                def build(sc):
+                    seen = set()
+                    for nd in operand.walk():
+                        if nd.k == "load" and nd.off.is_plain() and (nd.buf.root.id, nd.off.key()) not in seen:
+                            seen.add((nd.buf.root.id, nd.off.key()))
+                            sc.emit(f"anvil::prefetch_l2({self.ptr(nd.buf, False)} + ({sc.affine(nd.off, 0)}));")
+                    return None
+                return build
+            fa4 = fa4 + self.functor_method("void a_touch(int m, int k, int bt)", dm + dks + db, operand_touch(c.a))
+            fb4 = fb4 + self.functor_method("void b_touch(int k, int n, int bt)", dn + dks + db, operand_touch(c.b))
         pp = variant == "pp"
         pair = variant == "pair" or pp
         if pair:                                 # 256 x BN tile per cluster of two CTAs

@@ -890,6 +890,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
 //   tempty[b] in CTA 0, one arrival per epilogue warp of both CTAs once its tcgen05.ld are done.
 constexpr int PP_CONV_GROUPS = 2, PP_EPI_WARPS = 8;
 constexpr int PP_MMA_WARP = 8 * PP_CONV_GROUPS + PP_EPI_WARPS, PP_THREADS = 32 * PP_MMA_WARP + 32;
+constexpr int PP_AHEAD = 2;                                       // operand prefetch distance, in blocks of one converter group
 constexpr int PP_SLOTS = 74;                                      // clusters resident at once: one per SM pair
 __host__ __device__ constexpr uint32_t pp_smem_bytes() {
     return STAGES * pair_stage_bytes(256) + PP_EPI_WARPS * 32 * 33 * 4 + 256;
@@ -978,13 +979,39 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
                 else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
             }
         };
+        // L2 prefetch of a later block of the same item: one 128-byte line per 32 k of a row (operand contiguous
+        // along k), or per 32 rows at one k (operand contiguous along its rows); one lane per line asks.
+        auto touch = [&](const Item &it, int kb) {
+            if (kb >= it.nkb) return;
+            const int k0 = it.k_begin + kb * BK;
+#pragma unroll
+            for (int p = 0; p < BM / 32; p++) {
+                int row, kc;
+                TileMap<AK, BM>::at(tc, p, row, kc);
+                const int m = it.m0 + row, k = k0 + kc * 4;
+                if (m < M && k < it.k_end) {
+                    if (AK) { if (kc == 0) f.a_touch(m, k, it.bt); }
+                    else if (lane == 0) { f.a_touch(m, k, it.bt); f.a_touch(m, k + 1, it.bt); f.a_touch(m, k + 2, it.bt); f.a_touch(m, k + 3, it.bt); }
+                }
+            }
+#pragma unroll
+            for (int p = 0; p < BH / 32; p++) {
+                int row, kc;
+                TileMap<BKC, BH>::at(tc, p, row, kc);
+                const int n = it.nb0 + row, k = k0 + kc * 4;
+                if (n < N && k < it.k_end) {
+                    if (BKC) { if (kc == 0) f.b_touch(k, n, it.bt); }
+                    else if (lane == 0) { f.b_touch(k, n, it.bt); f.b_touch(k + 1, n, it.bt); f.b_touch(k + 2, n, it.bt); f.b_touch(k + 3, n, it.bt); }
+                }
+            }
+        };
         // (w, kb) of this group's current block; `advance` moves it G blocks on
         int w = cid, kb = grp;
         Item it = item(w < WORK ? w : 0);
         auto settle = [&]() { while (w < WORK && kb >= it.nkb) { kb -= it.nkb; w += ncl; if (w < WORK) it = item(w); } };
         settle();
         const uint32_t full_leader0 = map_to_cta(full(0), 0);
-        if (w < WORK) fetch(it, kb);
+        if (w < WORK) { fetch(it, kb); touch(it, kb + G); touch(it, kb + 2 * G); }
         for (long n = grp; w < WORK; n += G) {
             const int s = (int)(n % NST);
             const uint32_t ph = (uint32_t)(n / NST) & 1u;
@@ -1004,7 +1031,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
             }
             kb += G;
             settle();
-            if (w < WORK) fetch(it, kb);
+            if (w < WORK) { fetch(it, kb); touch(it, kb + PP_AHEAD * G); }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(full_leader0 + 8u * s);
