@@ -1042,7 +1042,7 @@ def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
            epilogue warps overlapping across tiles — needs M >= 256 and N >= 128; the default there
            (16384x2048x512: 232-245 TFLOP/s against 150-154 for "ss32");
     "pair" the same tile, one launch-time CTA pair per tile (kept for comparison);
-    "ts"   A tiles in tensor memory — when A is read along m and the output is small or narrow;
+    "ts"   A tiles in tensor memory — when A is read along m and the output is narrow;
     "ss"   operands in shared memory, 16-wide k blocks, two CTAs per SM — short reductions (K <= 128)
            on narrow outputs;
     "ss32" operands in shared memory, 32-wide k blocks, one CTA per SM — the remaining shapes."""
@@ -1053,7 +1053,7 @@ def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
         v = "1"
     if v in ("pair", "pp", "ss", "ts", "ss32"):
         return v
-    if pair_ok and (a_kcontig or M * N > 512 * 512):
+    if pair_ok:
         return "pp"
     if not a_kcontig:
         return "ts"

@@ -62,6 +62,16 @@ def test_free_running_trajectory(cfg):
     assert rel.max() <= 2e-2, (int(rel.argmax()), float(rel.max()))
 
 
+def test_full_size_c5_first_steps():
+    """The benchmark's own workload (6 layers, D 512, T 256, batch 64) against the reference interpreter run at
+    full size: two steps is what the interpreter finishes in five hours (tests/golden/c5_transformer.losses.json,
+    made by `make_golden.py traj c5_transformer 2`)."""
+    want = json.load(open(os.path.join(GOLDEN, "c5_transformer.losses.json")))["losses"]
+    got = free_running(kir.load(os.path.join(ROOT, "anvil_lang_b200", "programs", "c5_transformer.kir.json.gz")), len(want))
+    rel = np.abs(np.array(got) - np.array(want)) / np.abs(want)
+    assert rel.max() <= 1e-4, (got, want)
+
+
 @pytest.mark.parametrize("cfg", sorted(CONFIGS))
 def test_windowed_trajectory(cfg):
     path, _, steps = CONFIGS[cfg]
