@@ -952,7 +952,7 @@ class KernelGen:
         pp = variant == "pp"
         pair = variant == "pair" or pp
         if pair:                                 # 256 x BN tile per cluster of two CTAs
-            BN = 256 if N >= 256 or pp else 128
+            BN = 256 if N >= 256 else 128 if N >= 128 or not pp else 64
             tiles = ((M + 255) // 256) * ((N + BN - 1) // BN)
             slots = 74
         else:
@@ -965,7 +965,7 @@ class KernelGen:
         S = max(S, (K + 4095) // 4096)           # one accumulation chain stays <= 4096 long (rounding, see the header)
         AK = "true" if c.a_kcontig else "false"
         BKC = "true" if ct._contig(c.b, c.kvars[-1]) else "false"
-        src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (tcgen05 3xTF32, 128x{BN} tiles, split {S})"),
+        src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (tcgen05 3xTF32, {256 if pair else 128}x{BN} tiles, split {S})"),
                f"struct {fn} {{", "    char *__restrict__ A;",
                f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = {NB};",
                f"    static constexpr float ALPHA = {flit(c.alpha)};"] + fa4 + fb4 + fe + ["};"]
@@ -977,10 +977,10 @@ class KernelGen:
         grid_x = 2 * tiles if pair else tiles
         grid_y = NB * S
         if pp:                                   # resident clusters walk over (tile, batch, split) items
-            accs = 1 if (K + S - 1) // S <= 512 else 2
-            smem, threads, per_sm = "anvil::tc::pp_smem_bytes()", "anvil::tc::PP_THREADS", 1
+            accs = 1 if (K + S - 1) // S <= 512 and BN == 256 else 2
+            smem, threads, per_sm = f"anvil::tc::pp_smem_bytes({BN})", "anvil::tc::PP_THREADS", 1
             tile_fn = f"anvil::tc::gemm_tc_pair_persistent<{fn}, {AK}, {BKC}, "
-            tile_tail = f", {accs}>"
+            tile_tail = f", {accs}, {BN}>"
             attrs = "__cluster_dims__(2, 1, 1) "
             grid_x, grid_y = 2 * min(tiles * NB * S, 74), 1
         elif pair:
@@ -1049,11 +1049,12 @@ def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
     import os
     v = os.environ.get("ANVIL_B200_TC", "1")
     pair_ok = M >= 256 and N >= 128
-    if v in ("pair", "pp") and not pair_ok:
+    pp_ok = M >= 256 and N >= 64
+    if (v == "pair" and not pair_ok) or (v == "pp" and not pp_ok):
         v = "1"
     if v in ("pair", "pp", "ss", "ts", "ss32"):
         return v
-    if pair_ok:
+    if pp_ok:
         return "pp"
     if not a_kcontig:
         return "ts"

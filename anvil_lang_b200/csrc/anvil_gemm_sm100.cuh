@@ -892,22 +892,26 @@ constexpr int PP_CONV_GROUPS = 2, PP_EPI_WARPS = 8;
 constexpr int PP_MMA_WARP = 8 * PP_CONV_GROUPS + PP_EPI_WARPS, PP_THREADS = 32 * PP_MMA_WARP + 32;
 constexpr int PP_AHEAD = 2;                                       // operand prefetch distance, in blocks of one converter group
 constexpr int PP_SLOTS = 74;                                      // clusters resident at once: one per SM pair
-__host__ __device__ constexpr uint32_t pp_smem_bytes() {
-    return STAGES * pair_stage_bytes(256) + PP_EPI_WARPS * 32 * 33 * 4 + 256;
+__host__ __device__ constexpr uint32_t pp_smem_bytes(int bn = 256) {
+    return (STAGES * pair_stage_bytes(bn) > 82u * 1024u ? STAGES * pair_stage_bytes(bn) : 82u * 1024u)   // one CTA per SM: each takes all of TMEM
+           + PP_EPI_WARPS * 32 * 33 * 4 + 256;
 }
 
-template <class F, bool AK, bool BKC, int SPLIT, int ACCS>
+// BN = 256, 128 or 64 columns per tile (narrow outputs: the attention products with a 64-wide head). With BN <= 128
+// two accumulator pairs fit, so ACCS = 2 is double-buffered as well.
+template <class F, bool AK, bool BKC, int SPLIT, int ACCS, int BN = 256>
 __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__restrict__ partial, uint32_t *status) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int M = F::M, N = F::N, K = F::K;
-    constexpr int BN = 256, BH = 128;
+    constexpr int BH = BN / 2;
+    static_assert(BN == 256 || BN == 128 || BN == 64, "tile width");
     constexpr int TILES_N = (N + BN - 1) / BN, TILES = ((M + 2 * BM - 1) / (2 * BM)) * TILES_N;
     constexpr int WORK = TILES * F::NB * SPLIT;
-    constexpr int NBUF = ACCS == 1 ? 2 : 1;
+    constexpr int NBUF = ACCS * BN <= 256 ? 2 : 1;
     constexpr uint32_t BUF_COLS = ACCS * BN;
     constexpr uint32_t LBO_A = lbo_bytes(BM), LBO_B = lbo_bytes(BH);
     constexpr uint32_t TA = tile_bytes(BM), TB = tile_bytes(BH), STAGE = pair_stage_bytes(BN);
-    constexpr uint32_t EPI_OFF = STAGES * STAGE, BAR_OFF = pp_smem_bytes() - 256;
+    constexpr uint32_t BAR_OFF = pp_smem_bytes(BN) - 256, EPI_OFF = BAR_OFF - PP_EPI_WARPS * 32 * 33 * 4;
     constexpr int KCH = ((K + SPLIT - 1) / SPLIT + BK - 1) / BK * BK;
     constexpr int NST = STAGES, G = PP_CONV_GROUPS;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -1083,7 +1087,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         const int e = warp - 8 * G, q = warp & 3, half = e >> 2;
         float *stage_f = reinterpret_cast<float *>(smem + EPI_OFF) + e * (32 * 33);
         const uint32_t tempty_leader0 = map_to_cta(tempty(0), 0);
-        constexpr int CPW = (BN / 32) / (PP_EPI_WARPS / 4);                       // column chunks per warp
+        constexpr int CPW = (BN / 32) / (PP_EPI_WARPS / 4);                       // column chunks per warp (4, 2 or 1)
         // What the statements read besides the accumulator (a residual, the old value of a `+=`) is
         // asked into L2 one item ahead: lane = row, one 128-byte line per column chunk.
         auto touch = [&](const Item &it) {
