@@ -890,7 +890,7 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
 //   tempty[b] in CTA 0, one arrival per epilogue warp of both CTAs once its tcgen05.ld are done.
 constexpr int PP_CONV_GROUPS = 2, PP_EPI_WARPS = 8;
 constexpr int PP_MMA_WARP = 8 * PP_CONV_GROUPS + PP_EPI_WARPS, PP_THREADS = 32 * PP_MMA_WARP + 32;
-constexpr int PP_AHEAD = 2;                                       // operand prefetch distance, in blocks of one converter group
+constexpr int PP_AHEAD = 4;                                       // operand prefetch distance, in blocks of one converter group
 constexpr int PP_SLOTS = 74;                                      // clusters resident at once: one per SM pair
 __host__ __device__ constexpr uint32_t pp_smem_bytes(int bn = 256) {
     return (STAGES * pair_stage_bytes(bn) > 82u * 1024u ? STAGES * pair_stage_bytes(bn) : 82u * 1024u)   // one CTA per SM: each takes all of TMEM
@@ -1015,7 +1015,19 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         auto settle = [&]() { while (w < WORK && kb >= it.nkb) { kb -= it.nkb; w += ncl; if (w < WORK) it = item(w); } };
         settle();
         const uint32_t full_leader0 = map_to_cta(full(0), 0);
-        if (w < WORK) { fetch(it, kb); touch(it, kb + G); touch(it, kb + 2 * G); }
+        // a second cursor runs PP_AHEAD group turns in front of the first, across item boundaries, and asks L2 for its block
+        int tw = w, tkb = kb;
+        Item tit = it;
+        auto touch_next = [&]() {
+            tkb += G;
+            while (tw < WORK && tkb >= tit.nkb) { tkb -= tit.nkb; tw += ncl; if (tw < WORK) tit = item(tw); }
+            if (tw < WORK) touch(tit, tkb);
+        };
+        if (w < WORK) {
+            fetch(it, kb);
+#pragma unroll 1
+            for (int a = 0; a < PP_AHEAD; a++) touch_next();
+        }
         for (long n = grp; w < WORK; n += G) {
             const int s = (int)(n % NST);
             const uint32_t ph = (uint32_t)(n / NST) & 1u;
@@ -1035,7 +1047,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
             }
             kb += G;
             settle();
-            if (w < WORK) { fetch(it, kb); touch(it, kb + PP_AHEAD * G); }
+            if (w < WORK) { fetch(it, kb); touch_next(); }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(full_leader0 + 8u * s);

@@ -26,6 +26,7 @@ CASES = [
     (300, 300, 72, 2, True, False, True, False, 1.0, False, False),           # ragged in every direction, two tile columns
     (1024, 1024, 1024, 1, False, False, True, False, 1.0, False, False),
     (16384, 512, 2048, 1, False, False, True, False, 1.0, False, False),       # a transformer MLP product (A is 134 MB)
+    (256, 64, 256, 512, False, False, False, False, 1.0, False, False),        # attention P·V over 512 (batch, head) pairs
 ]
 
 
