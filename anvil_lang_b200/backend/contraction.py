@@ -136,6 +136,13 @@ def match(k: kir.Kernel, min_flops: int = 1 << 21) -> Contraction | None:
         # which factor is called A is arbitrary: the tiles are 128 rows of M by 64 or 128 columns of N,
         # so the short side goes to N
         side_a, side_b, mvars, nvars = side_b, side_a, nvars, mvars
+    elif min(kir.prod(v.extent for v in mvars), kir.prod(v.extent for v in nvars)) >= 128:
+        # both sides can be rows: let N run along the output's contiguous index, because the epilogue (and
+        # the split-k finish) puts consecutive lanes on consecutive n — a weight gradient stored as
+        # dW[n_features_in, n_features_out] with the factors the other way round had 32 sectors per store
+        outs = [s_ for s_ in k.stmts if isinstance(s_, kir.Store)]
+        if outs and outs[0].offset.is_plain() and outs[0].offset.coef(mvars[-1]) == 1 and outs[0].offset.coef(nvars[-1]) != 1:
+            side_a, side_b, mvars, nvars = side_b, side_a, nvars, mvars
     c = Contraction(k, mvars, nvars, kvars, bvars, _product([ops[i] for i in side_a]),
                     _product([ops[i] for i in side_b]), alpha, False, False)
     if c.M < 32 or c.N < 32 or c.K < 8 or c.flops < min_flops:

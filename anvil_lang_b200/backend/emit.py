@@ -848,21 +848,32 @@ class KernelGen:
         # Two-phase form of the statements: epi_loads fetches what they read at (m, n) — tensors this kernel
         # never writes, and the old value of an exclusive `+=` — and epi2 runs them on those values, so a
         # caller can issue the loads of several rows before the first store.
-        written = {st.buf.root.id for st in k.stmts if isinstance(st, kir.Store)}
+        # A per-element read may move in front of all stores when nothing can have written that element yet:
+        # the tensor is never stored by this kernel, or every store to it is exclusive, hits exactly the element
+        # read, and comes no earlier than the last statement that reads it (the old value of `+=`, the moments
+        # of an Adam update).
+        stores_of: dict = {}
+        for si, st in enumerate(k.stmts):
+            if isinstance(st, kir.Store):
+                stores_of.setdefault(st.buf.root.id, []).append((si, st))
+        reads: dict = {}                                     # (root, offset key) -> [buffer, offset, last reading statement]
+        for si, st in enumerate(k.stmts):
+            found = [(n.buf, n.off) for n in st.value.walk() if n.k == "load" and n.dt == F32]
+            if isinstance(st, kir.Store) and st.accumulate and st.buf.dtype == F32:
+                found.append((st.buf, st.offset))
+            for buf, off in found:
+                r = reads.setdefault((buf.root.id, off.key()), [buf, off, si])
+                r[2] = max(r[2], si)
         pre: list = []
-        for st in k.stmts:
-            cands = [(n.buf, n.off, False) for n in st.value.walk() if n.k == "load" and n.dt == F32]
-            if isinstance(st, kir.Store) and st.accumulate and st.buf.dtype == F32 and an.exclusive_store(k, st) \
-                    and sum(1 for x in k.stmts if isinstance(x, kir.Store) and x.buf.root.id == st.buf.root.id) == 1:
-                cands.append((st.buf, st.offset, True))
-            for buf, off, own in cands:
-                vs = off.vars()
-                if not off.is_plain() or not (any(v in vs for v in c.mvars) and any(v in vs for v in c.nvars)):
-                    continue
-                if (buf.root.id in written) != own or any(b.root.id == buf.root.id and o.key() == off.key() for b, o, _ in pre):
-                    continue
-                if len(pre) < 4:
-                    pre.append((buf, off, own))
+        for (root, okey), (buf, off, last_read) in reads.items():
+            vs = off.vars()
+            if not off.is_plain() or not (any(v in vs for v in c.mvars) and any(v in vs for v in c.nvars)):
+                continue
+            ok = all(sj >= last_read and st.offset.key() == okey and an.exclusive_store(k, st)
+                     for sj, st in stores_of.get(root, []))
+            other_reads = [key for key in reads if key[0] == root and key[1] != okey]
+            if ok and not (stores_of.get(root) and other_reads) and len(pre) < 4:
+                pre.append((buf, off, bool(stores_of.get(root))))
         nld = len(pre)
 
         def loads(sc):

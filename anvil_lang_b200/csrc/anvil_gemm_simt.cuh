@@ -123,10 +123,13 @@ __device__ __forceinline__ void gemm_split_finish(const F &f, const float *__res
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < MN * F::NB; i += (long)gridDim.x * blockDim.x) {
         const int bt = (int)(i / MN);
         const long mn = i % MN;
+        const int m = (int)(mn / F::N), n = (int)(mn % F::N);
+        float ld[F::NLD > 0 ? F::NLD : 1];
+        if (F::NLD > 0) f.epi_loads(m, n, bt, ld);          // what the statements read, before the first store
         float acc = 0.0f;
 #pragma unroll 4
         for (int s = 0; s < SPLIT; s++) acc += partial[((long)bt * SPLIT + s) * MN + mn];
-        f.epi((int)(mn / F::N), (int)(mn % F::N), bt, acc * F::ALPHA);
+        f.epi2(m, n, bt, acc * F::ALPHA, ld);
     }
 }
 
