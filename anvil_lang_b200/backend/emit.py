@@ -945,7 +945,8 @@ class KernelGen:
         db = self.decode("(uint32_t)bt", c.bvars, self.names, ind) if c.bvars else []
         fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
         fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
-        variant = tc_variant(c.a_kcontig, M, N, K)
+        nstores = sum(1 for st in k.stmts if isinstance(st, kir.Store))
+        variant = tc_variant(c.a_kcontig, M, N, K, nstores)
         if variant == "pp":                      # L2 prefetch of the operand element (m, k) / (k, n): issued some blocks ahead
             dks = self.decode("(uint32_t)k", c.kvars, self.names, ind)
 
@@ -1047,7 +1048,7 @@ def use_tensor_cores() -> bool:
     return os.environ.get("ANVIL_B200_TC", "1") != "0"
 
 
-def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
+def tc_variant(a_kcontig: bool, M: int, N: int, K: int, nstores: int = 1) -> str:
     """Which tcgen05 template a contraction takes (ANVIL_B200_TC=pp|pair|ss|ss32|ts forces one where it applies):
     "pp"   resident clusters of two CTAs on 256 x 256 tiles (tcgen05.mma.cta_group::2), converter / MMA /
            epilogue warps overlapping across tiles — needs M >= 256 and N >= 128; the default there
@@ -1065,6 +1066,8 @@ def tc_variant(a_kcontig: bool, M: int, N: int, K: int) -> str:
         v = "1"
     if v in ("pair", "pp", "ss", "ts", "ss32"):
         return v
+    if pp_ok and K <= 128 and nstores >= 2 and a_kcontig:
+        return "ss"                  # two blocks of main loop per tile and two outputs: all warps of "ss" store (34 vs 27 TFLOP/s)
     if pp_ok:
         return "pp"
     if not a_kcontig:
