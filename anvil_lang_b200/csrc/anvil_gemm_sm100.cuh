@@ -959,6 +959,55 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
     const uint32_t tmem = *tmem_slot;
     if (t == 0) { ANVIL_TC_TRACE(1); }
 
+    // One 32-row x 32-column piece of an accumulator buffer: tensor memory -> registers -> transposed through
+    // `stage_f` (32 x 33 floats of this warp) -> the statements, eight rows at a time: first everything the
+    // statements read, then the statements. release >= 0: hand tensor-memory buffer `release` back after the loads.
+    auto drain = [&](const Item &it, uint32_t acc, int c, float *stage_f, int release, uint32_t tempty_leader0) {
+        const int q = warp & 3;
+        uint32_t r[32];
+        tmem_ld32(acc + (uint32_t)(32 * c), r);
+        if (ACCS == 2) {
+            uint32_t r2[32];
+            tmem_ld32(acc + (uint32_t)(BN + 32 * c), r2);
+#pragma unroll
+            for (int x = 0; x < 32; x++) r[x] = __float_as_uint(__uint_as_float(r[x]) + __uint_as_float(r2[x]));
+        }
+        if (release >= 0) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8u * release);
+        }
+#pragma unroll
+        for (int x = 0; x < 32; x++) stage_f[lane * 33 + x] = __uint_as_float(r[x]);
+        __syncwarp();
+        const int n = it.n0 + 32 * c + lane;
+        constexpr int RB = 8, NLD = F::NLD > 0 ? F::NLD : 1;
+        for (int r0 = 0; r0 < 32; r0 += RB) {
+            const int mb = it.m0 + 32 * q + r0;
+            float ld[RB][NLD];
+            if (SPLIT == 1 && F::NLD > 0) {
+#pragma unroll
+                for (int rr = 0; rr < RB; rr++)
+                    if (mb + rr < M && n < N) f.epi_loads(mb + rr, n, it.bt, ld[rr]);
+            }
+#pragma unroll
+            for (int rr = 0; rr < RB; rr++) {
+                const int m = mb + rr;
+                const float v = stage_f[(r0 + rr) * 33 + lane];
+                if (m < M && n < N) {
+                    if (SPLIT > 1) partial[(((long)it.bt * SPLIT + it.sp) * M + m) * N + n] = v;
+                    else f.epi2(m, n, it.bt, v * F::ALPHA, ld[rr]);
+                }
+            }
+        }
+        __syncwarp();
+    };
+    // The cluster's last item has no main loop after it to hide its epilogue, and the converter warps are idle
+    // by then: its column chunks are dealt round-robin to the six warps of each lane quarter (two epilogue
+    // warps, four converter warps) instead of the two epilogue warps alone.
+    constexpr int NCH = BN / 32, LAST_WORKERS = 2 + 2 * G;
+    const int n_items = cid < WORK ? (WORK - cid + ncl - 1) / ncl : 0;
+
     if (warp < 8 * G) {
         // ---------------------------------------------------------------- converters
         const int grp = warp >> 3;
@@ -1052,6 +1101,18 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(full_leader0 + 8u * s);
         }
+        if (n_items > 0 && !*failed) {
+            const int il = n_items - 1, buf = il % NBUF;
+            if (mbar_wait(tfull(buf), ((uint32_t)(il / NBUF)) & 1u)) {       // every MMA is done: the stages are free
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const Item itl = item(cid + il * ncl);
+                const uint32_t acc = tmem + (uint32_t)buf * BUF_COLS + ((uint32_t)(32 * (warp & 3)) << 16);
+                float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);
+                for (int c = 2 + (warp >> 2); c < NCH; c += LAST_WORKERS) drain(itl, acc, c, stage_f, -1, 0u);
+            } else {
+                *failed = 1;
+            }
+        }
     } else if (warp == PP_MMA_WARP) {
         if (lane == 0 && rank == 0) {
             // ------------------------------------------------------------ MMA issuer (CTA 0 of the pair only)
@@ -1121,46 +1182,11 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
             if (w + ncl < WORK) touch(item(w + ncl));
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem + (uint32_t)buf * BUF_COLS + ((uint32_t)(32 * q) << 16);
-            for (int cc = 0; cc < CPW; cc++) {
-                const int c = half * CPW + cc;
-                uint32_t r[32];
-                tmem_ld32(acc + (uint32_t)(32 * c), r);
-                if (ACCS == 2) {
-                    uint32_t r2[32];
-                    tmem_ld32(acc + (uint32_t)(BN + 32 * c), r2);
-#pragma unroll
-                    for (int x = 0; x < 32; x++) r[x] = __float_as_uint(__uint_as_float(r[x]) + __uint_as_float(r2[x]));
-                }
-                if (cc == CPW - 1) {                             // this warp's part of the buffer is in registers: hand it back
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8u * buf);
-                }
-#pragma unroll
-                for (int x = 0; x < 32; x++) stage_f[lane * 33 + x] = __uint_as_float(r[x]);
-                __syncwarp();
-                const int n = it.n0 + 32 * c + lane;
-                // eight rows at a time: first everything the statements read, then the statements
-                constexpr int RB = 8, NLD = F::NLD > 0 ? F::NLD : 1;
-                for (int r0 = 0; r0 < 32; r0 += RB) {
-                    const int mb = it.m0 + 32 * q + r0;
-                    float ld[RB][NLD];
-                    if (SPLIT == 1 && F::NLD > 0) {
-#pragma unroll
-                        for (int rr = 0; rr < RB; rr++)
-                            if (mb + rr < M && n < N) f.epi_loads(mb + rr, n, it.bt, ld[rr]);
-                    }
-#pragma unroll
-                    for (int rr = 0; rr < RB; rr++) {
-                        const int m = mb + rr;
-                        const float v = stage_f[(r0 + rr) * 33 + lane];
-                        if (m < M && n < N) {
-                            if (SPLIT > 1) partial[(((long)it.bt * SPLIT + it.sp) * M + m) * N + n] = v;
-                            else f.epi2(m, n, it.bt, v * F::ALPHA, ld[rr]);
-                        }
-                    }
-                }
-                __syncwarp();
+            if (i == n_items - 1) {
+                for (int c = half; c < NCH; c += LAST_WORKERS) drain(it, acc, c, stage_f, -1, 0u);
+            } else {
+                for (int cc = 0; cc < CPW; cc++)                 // after the last chunk's loads the buffer goes back to the MMA warp
+                    drain(it, acc, half * CPW + cc, stage_f, cc == CPW - 1 ? buf : -1, tempty_leader0);
             }
         }
         if (e == 0 && lane == 0) { ANVIL_TC_TRACE(5); }
