@@ -4,7 +4,15 @@
 //   C[b, m, n] = epilogue(alpha * sum_k A[b, m, k] * B[b, k, n])        (same functor contract as
 //                                                                        anvil_gemm_simt.cuh)
 //
-// One CTA computes a 128 x BN tile. Twenty-five warps:
+// Five templates share the operand conversion, the two-accumulator scheme and the bounded waits:
+//   gemm_tc_tile             one CTA per 128 x BN tile, operands in shared memory, 32-wide k blocks (described next)
+//   gemm_tc_ts_tile          the same with the A tiles kept in tensor memory
+//   gemm_tc2_tile            16-wide k blocks, two CTAs per SM (short reductions on narrow outputs)
+//   gemm_tc_pair_tile        two CTAs of a cluster on one 256-row tile, tcgen05.mma.cta_group::2
+//   gemm_tc_pair_persistent  resident CTA pairs walking over the tiles with converter, MMA and epilogue warps
+//                            overlapping across tiles — what every contraction with M >= 256 and N >= 64 takes
+//
+// gemm_tc_tile: one CTA computes a 128 x BN tile. Twenty-five warps:
 //   warps 0-23 "converters" (three groups of eight; group g takes k blocks g, g + 3, ...): read operand values through the generated functor (so prologues such as
 //              max(x, 0), scales and gathers cost nothing extra), split every f32 x into
 //              hi = x with the low 13 mantissa bits cleared (exactly a TF32 value) and lo = x - hi
