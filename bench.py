@@ -33,7 +33,8 @@ WORKLOADS = {
 L2_BYTES = 126 << 20
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under
 # profiles/ (gemm_tc_pp_16384x512x2048.md, c5_transformer_step_launches.md), keyed by the kernel's strategy note
-NCU_TRAFFIC = {"gemm tc 1x16384x512x2048": 141.8e6 + 13.9e6, "gemm tc 1x512x512x16384": 67.3e6 + 5.0e6}
+NCU_TRAFFIC = {"gemm tc 1x16384x512x2048": 141.8e6 + 13.9e6, "gemm tc 1x512x512x16384": 67.3e6 + 5.0e6,
+               "gemm tc 1x16384x512x512": 34.6e6 + 0.6e6}
 
 
 def load_program(name):
