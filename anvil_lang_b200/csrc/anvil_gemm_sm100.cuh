@@ -934,6 +934,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
     auto empty = [&](int s) { return bar0 + 8u * (NST + s); };
     auto tfull = [&](int b) { return bar0 + 8u * (2 * NST + b); };
     auto tempty = [&](int b) { return bar0 + 8u * (2 * NST + 2 + b); };
+    const uint32_t alldone = smem_u32(smem + BAR_OFF + 112);                     // every MMA of this cluster has completed
 
     // One work item: which rows / columns / k range. All roles walk the same sequence w = cid, cid + ncl, ...
     struct Item { int m0, n0, nb0, bt, sp, k_begin, k_end, nkb; };
@@ -952,6 +953,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
     if (t == 0) {
         for (int s = 0; s < NST; s++) { mbar_init(full(s), 2 * 8); mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; b++) { mbar_init(tfull(b), 1); mbar_init(tempty(b), 2 * PP_EPI_WARPS); }
+        mbar_init(alldone, 1);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         ANVIL_TC_TRACE(0);
@@ -1111,7 +1113,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         }
         if (n_items > 0 && !*failed) {
             const int il = n_items - 1, buf = il % NBUF;
-            if (mbar_wait(tfull(buf), ((uint32_t)(il / NBUF)) & 1u)) {       // every MMA is done: the stages are free
+            if (mbar_wait(alldone, 0)) {                                     // every MMA is done: the stages are free
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const Item itl = item(cid + il * ncl);
                 const uint32_t acc = tmem + (uint32_t)buf * BUF_COLS + ((uint32_t)(32 * (warp & 3)) << 16);
@@ -1161,6 +1163,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
                 }
                 mma_commit_pair(tfull(buf));
             }
+            mma_commit_pair(alldone);                            // a barrier of its own: tfull's parity alone cannot tell the last use from an earlier one
             ANVIL_TC_TRACE(3);
         }
     } else {

@@ -27,6 +27,7 @@ CASES = [
     (1024, 1024, 1024, 1, False, False, True, False, 1.0, False, False),
     (16384, 512, 2048, 1, False, False, True, False, 1.0, False, False),       # a transformer MLP product (A is 134 MB)
     (256, 64, 256, 512, False, False, False, False, 1.0, False, False),        # attention P·V over 512 (batch, head) pairs
+    (256, 256, 64, 300, False, True, False, False, 0.125, False, False),       # Q·K^T shape: two k blocks per item, 4-5 items per cluster
 ]
 
 
