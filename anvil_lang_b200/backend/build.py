@@ -64,7 +64,7 @@ def build_runtime(force: bool = False) -> str:
         return RT_LIB
     cus = [p for p in srcs if p.endswith(".cu")]
     cmd = [nvcc(), "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS,
-           "-I", INCLUDE, "-I", CSRC, "-o", RT_LIB, *cus]
+           "-I", INCLUDE, "-I", CSRC, "-o", RT_LIB, *cus, "-lz"]
     _run(cmd)
     with open(stamp_file, "w") as f:
         f.write(stamp)
@@ -114,6 +114,8 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_ptr": (P, [P, Z]), "anvil_rt_arena_bytes": (Z, [P]), "anvil_rt_stream": (P, [P]),
         "anvil_rt_use_stream": (I, [P, P]), "anvil_rt_last_error": (c.c_char_p, [P]),
         "anvil_rt_set_error": (I, [P, c.c_char_p]),
+        "anvil_rt_load_idx": (I, [P, c.c_char_p, Z, L, L, I]), "anvil_rt_load_csv": (I, [P, c.c_char_p, Z, L, L]),
+        "anvil_rt_load_bytes": (I, [P, c.c_char_p, Z, L]), "anvil_rt_input": (I, [P, Z, c.POINTER(I)]),
         "anvil_rt_h2d": (I, [P, Z, P, Z]), "anvil_rt_d2h": (I, [P, P, Z, Z]),
         "anvil_rt_h2d_async": (I, [P, Z, P, Z]), "anvil_rt_d2h_async": (I, [P, P, Z, Z]),
         "anvil_rt_zero": (I, [P, Z, Z]), "anvil_rt_sync": (I, [P]),

@@ -1600,6 +1600,14 @@ class ProgramGen:
             return [f"RT(anvil_rt_save_npy(rt, {c_string(a['path'])}, {tab}, {len(a['header'])}L, {self.off(b)}, {4 * b.numel}L));"]
         if n == "load_npy":
             return [f"RT(anvil_rt_load_npy(rt, {c_string(a['path'])}, {self.off(b)}, {b.numel}L, {a['offset']}L, {a['kind']}, {a['size']}));"]
+        if n == "load_idx":
+            return [f"RT(anvil_rt_load_idx(rt, {c_string(a['path'])}, {self.off(b)}, {b.numel}L, {int(a['header'])}L, {1 if b.dtype == I32 else 0}));"]
+        if n == "load_csv":
+            return [f"RT(anvil_rt_load_csv(rt, {c_string(a['path'])}, {self.off(b)}, {b.numel}L, {int(a['skip'])}L));"]
+        if n == "load_bytes":
+            return [f"RT(anvil_rt_load_bytes(rt, {c_string(a['path'])}, {self.off(b)}, {b.numel}L));"]
+        if n == "input":                                     # the end of the input ends the program with status 0
+            return [f"{{ int eof_; RT(anvil_rt_input(rt, {self.off(b)}, &eof_)); if (eof_) {{ anvil_rt_flush(rt); return 1000; }} }}"]
         if n == "sleep":
             return [f"{{ float s_; RT(anvil_rt_read_f32(rt, {self.off(b)}, &s_)); anvil_rt_flush(rt); "
                     f"if (s_ > 0) usleep((useconds_t)(s_ * 1e6f)); }}"]

@@ -13,6 +13,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <time.h>
+#include <zlib.h>
 
 #include <map>
 #include <string>
@@ -322,6 +323,100 @@ extern "C" int anvil_rt_save_npy(anvil_rt *rt, const char *path, const unsigned 
     fwrite(host.data(), 1, (size_t)bytes, f);
     fclose(f);
     return 0;
+}
+
+static void emit(anvil_rt *rt, const char *s, int to_stderr);
+
+// ANVIL_DATA, when set, replaces the directory of every data file (anvil_host.h:134-141).
+static std::string data_path(const char *path) {
+    const char *dir = getenv("ANVIL_DATA");
+    if (!dir || !*dir) return path;
+    const char *name = strrchr(path, '/');
+    return std::string(dir) + "/" + (name ? name + 1 : path);
+}
+static const char *const BAD_SHAPE = "anvil: data file %s does not have the shape this program was compiled for";
+
+// An IDX file (plain or gzip): `header` bytes are skipped, then n unsigned bytes become f32 or i32
+// values (anvil_host.h:143-156; anvil/interp.py:243-251).
+extern "C" int anvil_rt_load_idx(anvil_rt *rt, const char *path0, size_t off, long n, long header, int is_int) {
+    const std::string path = data_path(path0);
+    gzFile f = gzopen(path.c_str(), "rb");
+    if (!f) return fail(rt, "anvil: cannot open data file %s", path.c_str());
+    std::vector<unsigned char> raw((size_t)(n > 0 ? n : 1)), skip((size_t)(header > 0 ? header : 1));
+    const bool ok = gzread(f, skip.data(), (unsigned)header) == (int)header && gzread(f, raw.data(), (unsigned)n) == (int)n;
+    gzclose(f);
+    if (!ok) return fail(rt, BAD_SHAPE, path.c_str());
+    std::vector<uint32_t> out((size_t)(n > 0 ? n : 1));
+    for (long i = 0; i < n; i++) {
+        if (is_int) { int32_t v = raw[i]; memcpy(&out[i], &v, 4); }
+        else { float v = (float)raw[i]; memcpy(&out[i], &v, 4); }
+    }
+    return anvil_rt_h2d(rt, off, out.data(), 4 * (size_t)n);
+}
+
+static bool read_file(const std::string &path, std::string &text) {
+    FILE *f = fopen(path.c_str(), "rb");
+    if (!f) return false;
+    char chunk[1 << 16];
+    size_t got;
+    while ((got = fread(chunk, 1, sizeof chunk, f)) > 0) text.append(chunk, got);
+    fclose(f);
+    return true;
+}
+
+// "[+-] digit ..." or "[+-] . digit ..." (anvil_host.h:172-177)
+static bool number_starts(const char *p) {
+    if (*p == '+' || *p == '-') p++;
+    if (*p == '.') p++;
+    return *p >= '0' && *p <= '9';
+}
+
+// The first n numbers of a text file after `skip` lines, whatever separates them (anvil_host.h:179-190).
+extern "C" int anvil_rt_load_csv(anvil_rt *rt, const char *path0, size_t off, long n, long skip) {
+    const std::string path = data_path(path0);
+    std::string text;
+    if (!read_file(path, text)) return fail(rt, "anvil: cannot open data file %s", path.c_str());
+    const char *p = text.c_str();
+    for (long s = 0; s < skip && *p; p++) if (*p == '\n') s++;
+    std::vector<float> out((size_t)(n > 0 ? n : 1));
+    long got = 0;
+    while (got < n && *p) {
+        if (number_starts(p)) { char *end; out[got++] = strtof(p, &end); p = end; }
+        else p++;
+    }
+    if (got < n) return fail(rt, BAD_SHAPE, path.c_str());
+    return anvil_rt_h2d(rt, off, out.data(), 4 * (size_t)n);
+}
+
+// Exactly n bytes, each becoming one i32 (anvil_host.h:192-197).
+extern "C" int anvil_rt_load_bytes(anvil_rt *rt, const char *path0, size_t off, long n) {
+    const std::string path = data_path(path0);
+    std::string text;
+    if (!read_file(path, text)) return fail(rt, "anvil: cannot open data file %s", path.c_str());
+    if ((long)text.size() != n) return fail(rt, BAD_SHAPE, path.c_str());
+    std::vector<int32_t> out((size_t)(n > 0 ? n : 1));
+    for (long i = 0; i < n; i++) out[i] = (unsigned char)text[i];
+    return anvil_rt_h2d(rt, off, out.data(), 4 * (size_t)n);
+}
+
+// One line of standard input: its first decimal number (NaN if it has none) goes to the f32 at `off`;
+// *eof = 1 at the end of the input, after a newline has been printed (anvil_host.h:286-300).
+extern "C" int anvil_rt_input(anvil_rt *rt, size_t off, int *eof) {
+    char line[256];
+    anvil_rt_flush(rt);
+    *eof = 0;
+    if (!fgets(line, sizeof line, stdin)) { emit(rt, "\n", 0); *eof = 1; return 0; }
+    float v = NAN;
+    for (char *p = line; *p; p++) {
+        if (number_starts(p)) {
+            char *q = p;
+            if (*q == '+' || *q == '-') q++;
+            if (q[0] == '0' && (q[1] == 'x' || q[1] == 'X')) q[1] = 0;          // decimal only
+            v = strtof(p, nullptr);
+            break;
+        }
+    }
+    return anvil_rt_set_f32(rt, off, v);
 }
 
 // n values from byte `offset` of a NumPy (or safetensors, kind + 16) file converted to 32 bits;

@@ -89,6 +89,19 @@ int anvil_rt_load(anvil_rt *rt, const char *path, const anvil_rt_ckpt *tab, long
 int anvil_rt_save_npy(anvil_rt *rt, const char *path, const unsigned char *header, long hlen,
                       size_t off, long bytes);
 int anvil_rt_load_npy(anvil_rt *rt, const char *path, size_t off, long n, long offset, int kind, int size);
+/* Data files of the other formats; the environment variable ANVIL_DATA, when set, replaces the directory of `path`
+ * (anvil/backend/anvil_host.h:134-141). Errors: "anvil: cannot open data file <path>" or "anvil: data file <path>
+ * does not have the shape this program was compiled for" through anvil_rt_last_error, status 1.
+ *   load_idx    IDX file, plain or gzip: skip `header` bytes, n unsigned bytes -> f32 (is_int 0) or i32
+ *               (anvil_host.h:143-156, anvil/interp.py:243-251)
+ *   load_csv    the first n numbers after `skip` lines of a text file, any separators (anvil_host.h:179-190)
+ *   load_bytes  a file of exactly n bytes, one i32 each (anvil_host.h:192-197)
+ *   input       one line of standard input, its first decimal number (NaN if none) -> the f32 at `off`;
+ *               *eof = 1 at the end of the input, after printing a newline (anvil_host.h:286-300) */
+int anvil_rt_load_idx(anvil_rt *rt, const char *path, size_t off, long n, long header, int is_int);
+int anvil_rt_load_csv(anvil_rt *rt, const char *path, size_t off, long n, long skip);
+int anvil_rt_load_bytes(anvil_rt *rt, const char *path, size_t off, long n);
+int anvil_rt_input(anvil_rt *rt, size_t off, int *eof);
 
 /* ---- output (anvil_host.h:76-132) ----------------------------------------------------------------
  * Text goes to stdout/stderr, or into a capture buffer when capture is on (tests, notebooks). */

@@ -260,8 +260,17 @@ class Oracle:
         else:
             self.out.write(text)
 
+    @staticmethod
+    def data_path(path: str) -> str:
+        """ANVIL_DATA, when set, replaces the directory of a data file (anvil/backend/anvil_host.h:134-141)."""
+        import os
+        d = os.environ.get("ANVIL_DATA")
+        return os.path.join(d, os.path.basename(path)) if d else path
+
     def rtcall(self, st: kir.RTCall):
         a, n = st.args, st.name
+        if n in ("load_idx", "load_bytes", "load_csv"):
+            a = dict(a, path=self.data_path(a["path"]))
         if n == "seed":
             self.seed = a["value"] & 0xFFFFFFFF
             self.stream = 0
@@ -337,6 +346,41 @@ class Oracle:
             with open(a["path"], "wb") as f:
                 f.write(bytes(a["header"]))
                 f.write(self.arr(b)[:b.numel].astype(np.int32 if b.dtype == I32 else np.float32).tobytes())
+        elif n == "load_idx":                               # anvil/interp.py:243-251
+            import gzip
+            b = a["buf"]
+            with open(a["path"], "rb") as f:
+                magic = f.read(2)
+            opener = gzip.open if magic == b"\x1f\x8b" else open
+            with opener(a["path"], "rb") as f:
+                f.read(a["header"])
+                raw = np.frombuffer(f.read(b.numel), dtype=np.uint8)
+            if raw.size != b.numel:
+                raise OracleRuntimeError(f"data file {a['path']} does not have the shape this program was compiled for")
+            self.arr(b)[:b.numel] = raw.astype(self.arr(b).dtype)
+        elif n == "load_bytes":                             # anvil/interp.py:257-267
+            b = a["buf"]
+            try:
+                raw = open(a["path"], "rb").read()
+            except OSError:
+                raise OracleRuntimeError(f"cannot open data file {a['path']}")
+            if len(raw) != b.numel:
+                raise OracleRuntimeError(f"data file {a['path']} does not have the shape this program was compiled for")
+            self.arr(b)[:b.numel] = np.frombuffer(raw, dtype=np.uint8)
+        elif n == "load_csv":                               # anvil/interp.py:289-305
+            import re
+            b = a["buf"]
+            try:
+                text = open(a["path"], encoding="utf-8", errors="replace").read()
+            except OSError:
+                raise OracleRuntimeError(f"cannot open data file {a['path']}")
+            pos = 0
+            for _ in range(a["skip"]):
+                pos = text.index("\n", pos) + 1
+            vals = re.findall(r"[+-]?(?:\d+\.?\d*|\.\d+)(?:[eE][+-]?\d+)?", text[pos:])
+            if len(vals) < b.numel:
+                raise OracleRuntimeError(f"data file {a['path']} does not have the shape this program was compiled for")
+            self.arr(b)[:b.numel] = np.array([float(v) for v in vals[:b.numel]], dtype=np.float32)
         elif n == "load_npy" and not (a["kind"] & 16):
             b = a["buf"]
             data = np.load(a["path"], allow_pickle=False)
