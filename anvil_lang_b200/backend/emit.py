@@ -1343,7 +1343,9 @@ class ProgramGen:
         self.group_src.append(src)
         self.group_notes.append(f"rowgroup x{len(kernels)} {forms[0].R}x{forms[0].N}")
         body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
-                "    uint32_t seed = anvil_rt_get_seed(rt);", "    uint32_t sdelta = 0;"] + ["    " + ln for ln in launch] + ["    return 0;"]
+                "    uint32_t seed = anvil_rt_get_seed(rt);", "    uint32_t sdelta = 0;",
+                f"    RT(anvil_rt_prof_begin(rt, PROF_GROUP0 + {idx}));"] + ["    " + ln for ln in launch] \
+            + [f"    RT(anvil_rt_prof_end(rt, PROF_GROUP0 + {idx}));", "    return 0;"]
         self.group_launchers.append(f"static int launch_group_{idx}(anvil_rt *rt) {{   // {' + '.join(k.name for k in kernels)}\n"
                                     + "\n".join(body) + "\n}")
         return idx
@@ -1383,7 +1385,9 @@ class ProgramGen:
         body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
                 "    uint32_t seed = anvil_rt_get_seed(rt);"]
         body.append("    uint32_t sdelta = " + ("anvil_rt_next_stream_delta(rt);" if kg.uses_rand else "0;"))
+        body.append(f"    RT(anvil_rt_prof_begin(rt, {idx}));")
         body += ["    " + ln for ln in launch]
+        body.append(f"    RT(anvil_rt_prof_end(rt, {idx}));")
         body.append("    return 0;")
         self.launchers.append(f"static int launch_{idx}(anvil_rt *rt) {{   // {k.name} {k.label}\n" + "\n".join(body) + "\n}")
         return idx
@@ -1627,6 +1631,14 @@ class ProgramGen:
                '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', '#include "anvil_gemm_sm100.cuh"', "",
                "#define RT(call) do { if ((call) != 0) return 1; } while (0)", ""]
         out += self.tables + [""]
+        # --profile: one row per launch unit, "name label strategy" like the native back end's "name label location"
+        names = [f"{k.name:<6} {k.label[:34]:<34} {note}" for k, note in zip(self.kernels, self.kernel_notes)]
+        by_idx = {idx: key for key, idx in self.groups.items()}
+        for gi, note in enumerate(self.group_notes):
+            names.append(f"{'g%d' % gi:<6} {'fused rows':<34} {note}")
+        out.append(f"#define PROF_GROUP0 {len(self.kernels)}")
+        out.append("static const char *const prof_names[] = {" + ", ".join(c_string(x) for x in names) + ("" if names else '""') + "};")
+        out.append("")
         out.append("static const char *const fault_messages[] = {\"\", " + ", ".join(c_string(m) for m in self.faults)
                    + ("" if self.faults else "\"\"") + "};")
         out += ["", "// ---------------------------------------------------------------- kernels"]
@@ -1651,7 +1663,8 @@ class ProgramGen:
         out += ['extern "C" int anvil_b200_main(anvil_rt *rt, int mode) {',
                 f"    anvil_rt_fault_messages(rt, fault_messages, {len(self.faults) + 1});"]
         out += main
-        out += ["    RT(anvil_rt_check_faults(rt));", "    anvil_rt_flush(rt);", "    return 0;", "}", ""]
+        out += ["    RT(anvil_rt_check_faults(rt));", f"    RT(anvil_rt_profile_report(rt, prof_names, {len(self.kernels) + len(self.groups)}));",
+                "    anvil_rt_flush(rt);", "    return 0;", "}", ""]
         out += ['extern "C" int anvil_b200_step(anvil_rt *rt) {   // one iteration of the training loop']
         if self.hot_body is not None:
             out += self.hot_body + ["    return 0;", "}"]

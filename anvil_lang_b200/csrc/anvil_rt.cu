@@ -49,6 +49,10 @@ struct anvil_rt {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     anvil_allreduce_fn allreduce = nullptr;
     void *allreduce_user = nullptr;
+    bool profile = false;           // time every launch unit (graphs off) and report at the end of the program
+    std::map<int, std::pair<double, long>> prof;      // slot -> (milliseconds, calls)
+    std::vector<int> prof_order;    // slots in the order they first ran
+    cudaEvent_t pe0 = nullptr, pe1 = nullptr;
 };
 
 static double now_seconds() {
@@ -612,6 +616,50 @@ extern "C" int anvil_rt_oob(anvil_rt *rt, const char *message, long long value) 
 
 // ---------------------------------------------------------------------------- launch-sequence capture
 extern "C" void anvil_rt_graphs(anvil_rt *rt, int on) { rt->graphs_on = on != 0; }
+
+// ---------------------------------------------------------------------------- --profile
+// The reference's native back end times every kernel and prints "time% ms calls kernel" when the program ends
+// (anvil/backend/aarch64.py:383-400, 921-927; runtime.s:1590-1671). Here a launch unit (a kernel, its split
+// finish, or a fused row group) is bracketed by two CUDA events on the program's stream.
+extern "C" void anvil_rt_profile(anvil_rt *rt, int on) {
+    rt->profile = on != 0;
+    if (on) rt->graphs_on = false;                   // a replayed graph has no per-kernel boundaries
+}
+extern "C" int anvil_rt_prof_begin(anvil_rt *rt, int slot) {
+    if (!rt->profile) return 0;
+    (void)slot;
+    if (!rt->pe0) { CK(rt, cudaEventCreate(&rt->pe0)); CK(rt, cudaEventCreate(&rt->pe1)); }
+    CK(rt, cudaEventRecord(rt->pe0, rt->stream));
+    return 0;
+}
+extern "C" int anvil_rt_prof_end(anvil_rt *rt, int slot) {
+    if (!rt->profile) return 0;
+    CK(rt, cudaEventRecord(rt->pe1, rt->stream));
+    CK(rt, cudaEventSynchronize(rt->pe1));
+    float ms = 0;
+    CK(rt, cudaEventElapsedTime(&ms, rt->pe0, rt->pe1));
+    auto it = rt->prof.find(slot);
+    if (it == rt->prof.end()) { rt->prof_order.push_back(slot); it = rt->prof.emplace(slot, std::make_pair(0.0, 0L)).first; }
+    it->second.first += ms;
+    it->second.second += 1;
+    return 0;
+}
+extern "C" int anvil_rt_profile_report(anvil_rt *rt, const char *const *names, int n) {
+    if (!rt->profile || rt->prof_order.empty()) return 0;
+    double total = 0;
+    for (auto &kv : rt->prof) total += kv.second.first;
+    char line[512];
+    emit(rt, "\n  time%        ms      calls   kernel\n", 0);
+    for (int slot : rt->prof_order) {
+        const auto &r = rt->prof[slot];
+        snprintf(line, sizeof line, "%6.1f%%  %8.1f  %9lld   %s\n", 100.0 * r.first / (total > 0 ? total : 1.0), r.first,
+                 (long long)r.second, slot < n ? names[slot] : "?");
+        emit(rt, line, 0);
+    }
+    snprintf(line, sizeof line, "          %8.1f ms in kernels\n", total);
+    emit(rt, line, 0);
+    return 0;
+}
 extern "C" long anvil_rt_launch_count(anvil_rt *rt) { return rt->launches; }
 extern "C" void anvil_rt_count_launches(anvil_rt *rt, long n) { rt->launches += n; }
 

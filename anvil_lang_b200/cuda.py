@@ -43,12 +43,14 @@ def build(source: str, exe: str, emulate: bool = False):
     _build.build_program(source, exe)
 
 
-def run(prog, seed: int = 0, capture: bool = False, device: int = 0, graphs: bool = True):
+def run(prog, seed: int = 0, capture: bool = False, device: int = 0, graphs: bool = True, profile: bool = False):
     """Compile (cached) and execute on the device. Returns the exit status — 0, 1 after a run-time
     error (message on stderr, as `anvil: runtime error: ...`), or the value of a failed `assert` —
     and, with capture=True, the text the program printed."""
     dp = DeviceProgram(as_kir(prog), seed=seed, device=device, graphs=graphs)
     try:
+        if profile:                                      # `anvil run --profile` (anvil/cli.py:43): per-kernel table at the end
+            dp.rtlib.anvil_rt_profile(dp.rt, 1)
         code, text = dp.run(capture=capture)
         if code == 1 and dp.error:
             sys.stdout.flush()
@@ -67,6 +69,7 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--emit", action="store_true", help="print the generated CUDA instead of running")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="time every kernel and print a breakdown at exit")
     args = ap.parse_args(argv)
     if args.file.endswith((".json", ".json.gz")):
         prog = kir.load(args.file)
@@ -76,7 +79,7 @@ def main(argv=None) -> int:
     if args.emit:
         print(generate(prog, args.seed))
         return 0
-    return run(prog, seed=args.seed, graphs=not args.no_graphs)
+    return run(prog, seed=args.seed, graphs=not args.no_graphs, profile=args.profile)
 
 
 if __name__ == "__main__":

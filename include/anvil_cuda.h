@@ -132,6 +132,17 @@ int anvil_rt_graph_begin(anvil_rt *rt, int key);   /* 0: replayed a cached graph
                                                     <0: error */
 int anvil_rt_graph_end(anvil_rt *rt, int key);
 void anvil_rt_graphs(anvil_rt *rt, int on);
+/* --profile (reference: the native back end's per-kernel table, anvil/backend/aarch64.py:383-400, 921-927 and
+ * runtime.s:1590-1671; `anvil run --profile`, anvil/cli.py:43). With profiling on, graphs are off, every launch
+ * unit of a generated program brackets itself with prof_begin / prof_end (two CUDA events and a synchronise; no-ops
+ * otherwise), and the program's main prints
+ *     "\n  time%        ms      calls   kernel\n"  then  "%6.1f%%  %8.1f  %9lld   %s\n" per unit in first-run order
+ *     and  "          %8.1f ms in kernels\n"
+ * through profile_report before it returns. */
+void anvil_rt_profile(anvil_rt *rt, int on);
+int anvil_rt_prof_begin(anvil_rt *rt, int slot);
+int anvil_rt_prof_end(anvil_rt *rt, int slot);
+int anvil_rt_profile_report(anvil_rt *rt, const char *const *names, int n);
 long anvil_rt_launch_count(anvil_rt *rt);          /* kernels launched (graph replays count their nodes) */
 void anvil_rt_count_launches(anvil_rt *rt, long n);
 
