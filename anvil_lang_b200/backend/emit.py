@@ -1345,7 +1345,7 @@ class ProgramGen:
         body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
                 "    uint32_t seed = anvil_rt_get_seed(rt);", "    uint32_t sdelta = 0;",
                 f"    RT(anvil_rt_prof_begin(rt, PROF_GROUP0 + {idx}));"] + ["    " + ln for ln in launch] \
-            + [f"    RT(anvil_rt_prof_end(rt, PROF_GROUP0 + {idx}));", "    return 0;"]
+            + [f"    RT(anvil_rt_prof_end(rt, PROF_GROUP0 + {idx}));"] + self.check_lines(kernels) + ["    return 0;"]
         self.group_launchers.append(f"static int launch_group_{idx}(anvil_rt *rt) {{   // {' + '.join(k.name for k in kernels)}\n"
                                     + "\n".join(body) + "\n}")
         return idx
@@ -1388,9 +1388,28 @@ class ProgramGen:
         body.append(f"    RT(anvil_rt_prof_begin(rt, {idx}));")
         body += ["    " + ln for ln in launch]
         body.append(f"    RT(anvil_rt_prof_end(rt, {idx}));")
+        body += self.check_lines([k])
         body.append("    return 0;")
         self.launchers.append(f"static int launch_{idx}(anvil_rt *rt) {{   // {k.name} {k.label}\n" + "\n".join(body) + "\n}")
         return idx
+
+    def check_lines(self, kernels) -> list[str]:
+        """--check: after a launch unit, every f32 tensor it wrote is scanned for nan / infinity (the reference
+        does it kernel by kernel, anvil/interp.py:408-423); the message names the kernel that wrote the tensor."""
+        out, seen = [], set()
+        for k in kernels:
+            desc = f"  made by `{k.label or 'a computation'}`:\n  computing ({k.name}):  {kir.fmt_kernel(k)}"
+            for st in k.stores:
+                r = st.buf.root
+                if r.dtype != F32 or r.id in seen:
+                    continue
+                seen.add(r.id)
+                shp = self.table("long", [str(d) for d in r.shape]) if r.shape else "nullptr"
+                out.append(f"        RT(anvil_rt_check_tensor(rt, {self.off(r)}, {r.numel}L, {c_string(r.name)}, {shp}, "
+                           f"{len(r.shape)}, {c_string(desc)}));")
+        if not out:
+            return []
+        return ["    if (anvil_rt_checking(rt)) {"] + out + ["    }"]
 
     # ---- host control flow (anvil/backend/cuda.py:429-473)
     def block(self, b: kir.Block, ind: str, in_loop: bool, tail: list[str] | None = None, skip=()) -> list[str]:

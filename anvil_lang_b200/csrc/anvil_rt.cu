@@ -49,6 +49,7 @@ struct anvil_rt {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     anvil_allreduce_fn allreduce = nullptr;
     void *allreduce_user = nullptr;
+    int check = 0;                  // --check: 1 = nan, 2 = nan or infinity, scanned after every launch unit
     bool profile = false;           // time every launch unit (graphs off) and report at the end of the program
     std::map<int, std::pair<double, long>> prof;      // slot -> (milliseconds, calls)
     std::vector<int> prof_order;    // slots in the order they first ran
@@ -616,6 +617,50 @@ extern "C" int anvil_rt_oob(anvil_rt *rt, const char *message, long long value) 
 
 // ---------------------------------------------------------------------------- launch-sequence capture
 extern "C" void anvil_rt_graphs(anvil_rt *rt, int on) { rt->graphs_on = on != 0; }
+
+// ---------------------------------------------------------------------------- --check
+// The reference stops at the first nan (or infinity) a kernel writes and says where and by what
+// (anvil/interp.py:408-423; anvil/backend/aarch64.py:82-89, 459-481). Here every launch unit of a generated
+// program calls check_tensor for each f32 tensor it wrote; a scan kernel keeps the smallest bad index.
+__global__ void anvil_scan_bad(const float *__restrict__ p, long n, int mode, unsigned long long *first) {
+    unsigned long long best = ~0ull;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        const float v = p[i];
+        const bool bad = mode == 1 ? (v != v) : !(fabsf(v) <= 3.402823466e38f);
+        if (bad) { best = (unsigned long long)i; break; }           // this thread's indices only grow
+    }
+    if (best != ~0ull) atomicMin(first, best);
+}
+extern "C" void anvil_rt_check(anvil_rt *rt, int mode) {
+    rt->check = mode;
+    if (mode) rt->graphs_on = false;
+}
+extern "C" int anvil_rt_checking(anvil_rt *rt) { return rt->check; }
+extern "C" int anvil_rt_check_tensor(anvil_rt *rt, size_t off, long n, const char *name, const long *shape, int rank,
+                                     const char *made_by) {
+    if (!rt->check || n <= 0) return 0;
+    unsigned long long *first = (unsigned long long *)(rt->arena + ANVIL_RT_CHECK_OFF);
+    CK(rt, cudaMemsetAsync(first, 0xFF, 8, rt->stream));
+    const int blocks = (int)(n / 256 + 1 < 1184 ? n / 256 + 1 : 1184);
+    anvil_scan_bad<<<blocks, 256, 0, rt->stream>>>((const float *)(rt->arena + off), n, rt->check, first);
+    unsigned long long idx = ~0ull;
+    CK(rt, cudaMemcpyAsync(&idx, first, 8, cudaMemcpyDeviceToHost, rt->stream));
+    CK(rt, cudaStreamSynchronize(rt->stream));
+    if (idx == ~0ull) return 0;
+    float v = 0;
+    CK(rt, cudaMemcpy(&v, rt->arena + off + 4 * idx, 4, cudaMemcpyDeviceToHost));
+    std::string where;
+    if (rank > 0) {
+        std::vector<long> ix((size_t)rank);
+        unsigned long long r = idx;
+        for (int d = rank - 1; d >= 0; d--) { ix[d] = (long)(r % (unsigned long long)shape[d]); r /= (unsigned long long)shape[d]; }
+        where = " at [";
+        for (int d = 0; d < rank; d++) where += (d ? ", " : "") + std::to_string(ix[d]);
+        where += "]";
+    }
+    const char *what = v != v ? "nan" : (v > 0 ? "inf" : "-inf");
+    return fail(rt, "anvil: runtime error: --check: %s in `%s`%s\n%s", what, name, where.c_str(), made_by);
+}
 
 // ---------------------------------------------------------------------------- --profile
 // The reference's native back end times every kernel and prints "time% ms calls kernel" when the program ends

@@ -43,7 +43,8 @@ def build(source: str, exe: str, emulate: bool = False):
     _build.build_program(source, exe)
 
 
-def run(prog, seed: int = 0, capture: bool = False, device: int = 0, graphs: bool = True, profile: bool = False):
+def run(prog, seed: int = 0, capture: bool = False, device: int = 0, graphs: bool = True, profile: bool = False,
+        check: str | None = None):
     """Compile (cached) and execute on the device. Returns the exit status — 0, 1 after a run-time
     error (message on stderr, as `anvil: runtime error: ...`), or the value of a failed `assert` —
     and, with capture=True, the text the program printed."""
@@ -51,6 +52,8 @@ def run(prog, seed: int = 0, capture: bool = False, device: int = 0, graphs: boo
     try:
         if profile:                                      # `anvil run --profile` (anvil/cli.py:43): per-kernel table at the end
             dp.rtlib.anvil_rt_profile(dp.rt, 1)
+        if check:                                        # `anvil run --check[=inf]` (anvil/interp.py:408-423)
+            dp.rtlib.anvil_rt_check(dp.rt, 2 if check == "inf" else 1)
         code, text = dp.run(capture=capture)
         if code == 1 and dp.error:
             sys.stdout.flush()
@@ -70,6 +73,7 @@ def main(argv=None) -> int:
     ap.add_argument("--emit", action="store_true", help="print the generated CUDA instead of running")
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--profile", action="store_true", help="time every kernel and print a breakdown at exit")
+    ap.add_argument("--check", nargs="?", const="nan", choices=["nan", "inf"], help="stop at the first nan (or infinity) a kernel writes")
     args = ap.parse_args(argv)
     if args.file.endswith((".json", ".json.gz")):
         prog = kir.load(args.file)
@@ -79,7 +83,7 @@ def main(argv=None) -> int:
     if args.emit:
         print(generate(prog, args.seed))
         return 0
-    return run(prog, seed=args.seed, graphs=not args.no_graphs, profile=args.profile)
+    return run(prog, seed=args.seed, graphs=not args.no_graphs, profile=args.profile, check=args.check)
 
 
 if __name__ == "__main__":

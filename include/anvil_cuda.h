@@ -29,6 +29,7 @@ extern "C" {
 #define ANVIL_RT_FAULT_OFF 0        /* struct { int code; int pad; long long value; }            */
 #define ANVIL_RT_STREAM_OFF 16      /* uint32: device copy of the random stream counter           */
 #define ANVIL_RT_STATUS_OFF 32      /* uint32: status word written by kernels that give up a wait */
+#define ANVIL_RT_CHECK_OFF 48       /* uint64: smallest bad index found by the last --check scan     */
 
 typedef struct anvil_rt anvil_rt;
 
@@ -139,6 +140,15 @@ void anvil_rt_graphs(anvil_rt *rt, int on);
  *     "\n  time%        ms      calls   kernel\n"  then  "%6.1f%%  %8.1f  %9lld   %s\n" per unit in first-run order
  *     and  "          %8.1f ms in kernels\n"
  * through profile_report before it returns. */
+/* --check (reference: `anvil run --check[=inf]`, anvil/interp.py:408-423; aarch64.py:82-89, 459-481): mode 1 stops at
+ * the first nan, mode 2 at the first nan or infinity, in any f32 tensor a launch unit wrote. Graphs are off. Every
+ * launch unit of a generated program calls check_tensor for the tensors it wrote (a no-op when checking is off);
+ * a hit gives status 1 and the message
+ *     "anvil: runtime error: --check: nan in `name` at [i, j]\n  made by `label`:\n  computing (k12):  ..." */
+void anvil_rt_check(anvil_rt *rt, int mode);
+int anvil_rt_checking(anvil_rt *rt);
+int anvil_rt_check_tensor(anvil_rt *rt, size_t off, long n, const char *name, const long *shape, int rank,
+                          const char *made_by);
 void anvil_rt_profile(anvil_rt *rt, int on);
 int anvil_rt_prof_begin(anvil_rt *rt, int slot);
 int anvil_rt_prof_end(anvil_rt *rt, int slot);

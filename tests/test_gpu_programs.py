@@ -58,3 +58,30 @@ def test_profile_table_has_the_reference_layout():
     assert abs(sum(shares) - 100.0) < 1.0
     calls = {r.split()[3]: int(r.split()[2]) for r in rows}
     assert max(calls.values()) >= 10                              # the training loop's kernels ran once per step
+
+
+def test_check_stops_at_the_first_nan_and_says_where():
+    """`--check`: log of a negative number makes a nan; the run stops after the kernel that wrote it with the
+    reference's message head (anvil/interp.py:408-423) — `--check: nan in `name` at [indices]` — and the kernel."""
+    from anvil_lang_b200 import cuda
+    from anvil_lang_b200.kir import F32, Affine, Buffer, E, Kernel, KernelStmt, Store, Var
+    from kirbuild import nid
+    x = Buffer(nid(), "x", (3, 5), F32, "temp")
+    y = Buffer(nid(), "y", (3, 5), F32, "temp")
+    i, j = Var(nid(), "i", 3), Var(nid(), "j", 5)
+    at = Affine(0, [(i, 5), (j, 1)])
+    idx = E("un", F32, op="f32", a=[E("index", kir.I32, off=Affine(-7, [(i, 5), (j, 1)]))])      # negative for the first 7 elements
+    k1 = Kernel(nid(), "k1", "fill", [i, j], [Store(x, at, E("bin", F32, op="sub", a=[E("const", F32, val=0.5), idx]), False)], None)
+    k2 = Kernel(nid(), "k2", "log", [i, j], [Store(y, at, E("un", F32, op="log", a=[E("load", F32, buf=x, off=at)]), False)], None)
+    prog = kir.Program(kir.Block([KernelStmt(k1), KernelStmt(k2)]), [x, y], "check")
+    dp = DeviceProgram(prog, seed=0)
+    try:
+        assert dp.run(capture=True)[0] == 0                          # without --check the nans go unnoticed
+        dp.rtlib.anvil_rt_check(dp.rt, 1)
+        code, _ = dp.run(capture=True)
+        assert code == 1
+        head = dp.error.split("\n")
+        assert head[0] == "anvil: runtime error: --check: nan in `y` at [1, 3]", dp.error    # x = 0.5 - (5i + j - 7) < 0 from element 8 on
+        assert head[1] == "  made by `log`:" and head[2].startswith("  computing (k2):")
+    finally:
+        dp.close()
