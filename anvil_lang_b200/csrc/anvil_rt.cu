@@ -155,6 +155,17 @@ extern "C" int anvil_rt_h2d_async(anvil_rt *rt, size_t off, const void *src, siz
     CK(rt, cudaMemcpyAsync(rt->arena + off, src, bytes, cudaMemcpyHostToDevice, rt->stream));
     return 0;
 }
+// Device-to-device copy into the arena from memory another library owns (a `__cuda_array_interface__`
+// argument of anvil.function): waits for the producer first — its stream when the interface names one
+// (`producer_stream` != 0), the whole device otherwise — then copies on the program's stream.
+extern "C" int anvil_rt_d2d_async(anvil_rt *rt, size_t off, const void *src_device, size_t bytes, void *producer_stream) {
+    if (off + bytes > rt->arena_bytes) return fail(rt, "anvil: copy outside the arena");
+    if (producer_stream) CK(rt, cudaStreamSynchronize((cudaStream_t)producer_stream));
+    else CK(rt, cudaDeviceSynchronize());
+    CK(rt, cudaMemcpyAsync(rt->arena + off, src_device, bytes, cudaMemcpyDeviceToDevice, rt->stream));
+    return 0;
+}
+
 extern "C" int anvil_rt_d2h_async(anvil_rt *rt, void *dst, size_t off, size_t bytes) {
     if (in_range(rt, off, bytes)) return 1;
     CK(rt, cudaMemcpyAsync(dst, rt->arena + off, bytes, cudaMemcpyDeviceToHost, rt->stream));

@@ -29,10 +29,38 @@ from .program import AnvilRuntimeError, DeviceProgram
 LOWERED_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "programs", "lowered")
 
 
+class DeviceArray:
+    """A tensor argument that already lives in GPU memory (`__cuda_array_interface__`: torch, CuPy, Numba):
+    it is copied device-to-device into the arena, with no trip through the host."""
+
+    def __init__(self, obj):
+        cai = obj.__cuda_array_interface__
+        self.keep = obj
+        self.shape = tuple(int(d) for d in cai["shape"])
+        t = np.dtype(cai["typestr"])
+        if t == np.float32:
+            self.dtype = kir.F32
+        elif t == np.int32:
+            self.dtype = kir.I32
+        else:
+            raise TypeError(f"anvil: a device array of {t} cannot be passed without a copy (use float32 or int32)")
+        if cai.get("strides") is not None:
+            raise TypeError("anvil: a device array argument must be contiguous (row-major)")
+        self.ptr = int(cai["data"][0])
+        self.nbytes = 4 * int(np.prod(self.shape, dtype=np.int64))
+        st = cai.get("stream")
+        self.stream = int(st) if isinstance(st, int) and st > 2 else 0      # 1 / 2: the default streams
+
+
 def arguments(args):
-    """NumPy arrays for the tensor arguments, and the signature that picks the compiled version."""
+    """NumPy arrays (or DeviceArray) for the tensor arguments, and the signature that picks the compiled version."""
     tensors, sig = [], []
     for a in args:
+        if hasattr(a, "__cuda_array_interface__"):
+            d = DeviceArray(a)
+            tensors.append(d)
+            sig.append(("tensor", d.shape, d.dtype))
+            continue
         if isinstance(a, (bool, int, float, str)) and not isinstance(a, np.generic):
             if isinstance(a, bool):
                 text = "true" if a else "false"
@@ -147,8 +175,12 @@ class Compiled:
         results = [None if b is None else np.empty(b.shape, np.float32 if b.dtype == kir.F32 else np.int32)
                    for b in self.outputs]
         with self.lock:
-            for s, a in zip(self.in_slots, arrays):
-                if s is not None:
+            for s, a, b in zip(self.in_slots, arrays, self.inputs):
+                if s is None:
+                    continue
+                if isinstance(a, DeviceArray):               # already on the GPU: device-to-device, the slot stays empty
+                    self.dp._check(self.dp.rtlib.anvil_rt_d2d_async(self.dp.rt, self.dp.plan.off(b), a.ptr, a.nbytes, a.stream))
+                else:
                     s.value = a.ctypes.data
             for s, r in zip(self.out_slots, results):
                 if s is not None:

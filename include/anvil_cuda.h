@@ -49,6 +49,9 @@ int anvil_rt_set_error(anvil_rt *rt, const char *message);    /* returns 1      
 /* ---- data movement (replaces direct host access to unified memory) ---------------------------- */
 int anvil_rt_h2d(anvil_rt *rt, size_t off, const void *src, size_t bytes);   /* synchronous         */
 int anvil_rt_d2h(anvil_rt *rt, void *dst, size_t off, size_t bytes);         /* synchronous         */
+/* From device memory owned by someone else (a `__cuda_array_interface__` argument of anvil.function; the
+ * reference's pyapi has host arrays only, anvil/pyapi.py:276-296): waits for `producer_stream` (0: the device). */
+int anvil_rt_d2d_async(anvil_rt *rt, size_t off, const void *src_device, size_t bytes, void *producer_stream);
 int anvil_rt_h2d_async(anvil_rt *rt, size_t off, const void *pinned_src, size_t bytes);
 int anvil_rt_d2h_async(anvil_rt *rt, void *pinned_dst, size_t off, size_t bytes);
 int anvil_rt_zero(anvil_rt *rt, size_t off, size_t bytes);

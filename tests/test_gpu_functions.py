@@ -70,3 +70,21 @@ def test_full_size_matches_float64_formula(name):
     got = f(*args)
     assert close(got, formula(name, args))
     assert all(np.array_equal(a, b) for a, b in zip(args, before))      # arguments are never written
+
+
+def test_device_arrays_are_taken_without_a_host_copy():
+    """Arguments that expose `__cuda_array_interface__` (torch tensors here) go device-to-device into the arena;
+    the result equals the one computed from the same values passed as NumPy arrays, and mixing both works."""
+    import torch
+    f = pyapi.function(SOURCES["ln"], name="ln")
+    args = inputs("ln", True)
+    want = f(*args)
+    dev = [torch.from_numpy(a).cuda() for a in args]
+    got = f(*dev)
+    assert np.array_equal(got, want)
+    mixed = f(dev[0], args[1], dev[2])
+    assert np.array_equal(mixed, want)
+    assert len(f.versions) == 1                                    # same shapes and dtypes: the same compiled version
+    assert all(torch.equal(d.cpu(), torch.from_numpy(a)) for d, a in zip(dev, args))     # arguments are never written
+    with pytest.raises(TypeError):
+        f(dev[0].double(), args[1], args[2])
