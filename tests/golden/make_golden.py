@@ -1,7 +1,7 @@
 """Generates the golden fixtures from the reference implementation itself.
 
-Runs only where the reference checkout is present (pass its path with --reference, default
-/root/reference): it imports the reference's front end and NumPy interpreter, and writes
+Runs only where the reference checkout is present (pass its path with --reference, or set
+ANVIL_REFERENCE): it imports the reference's front end and NumPy interpreter, and writes
 
   programs   tests/golden/<name>.kir.json.gz   the optimized IR of tests/programs/<name>.anvil
              tests/golden/<name>.out.txt       what the reference interpreter printed
@@ -217,7 +217,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["programs", "configs", "functions", "traj", "dp"])
     ap.add_argument("args", nargs="*")
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("ANVIL_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")))
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     os.environ.setdefault("ANVIL_CACHE", "/tmp/anvil_cache")

@@ -5,7 +5,7 @@ pre-activation lands within an ulp of zero, two correct f32 implementations that
 order put it on different sides of the kink, one mask element flips, and the trajectories separate
 for good. The reference interpreter itself, re-run with its parameters perturbed by one ulp, drifts
 from its own recorded trajectory by 5e-4 (C4, step 24) and 5e-3 (C3, step 68) — measured with the CPU
-oracle, see DESIGN.md. So:
+oracle. So:
 
   * windowed: every 10 steps the device state is re-synchronised from the oracle running alongside;
     inside each window every loss must match the oracle's to 1e-3 (the project's trajectory bar);
