@@ -965,6 +965,8 @@ class KernelGen:
         pair = variant == "pair" or pp
         if pair:                                 # 256 x BN tile per cluster of two CTAs
             BN = 256 if N >= 256 else 128 if N >= 128 or not pp else 64
+            if pp and BN == 256 and K <= 1024 and ((M + 255) // 256) * ((N + 255) // 256) * NB < 74:
+                BN = 128                         # too few 256-wide tiles for the 74 clusters: narrower tiles before any k split
             tiles = ((M + 255) // 256) * ((N + BN - 1) // BN)
             slots = 74
         else:

@@ -42,7 +42,7 @@ def test_forced_variant_falls_back_when_the_shape_is_too_small():
 
 @pytest.mark.parametrize("case,bn,accs,split", [
     ((16384, 512, 2048, 1, False, False, True, False, 1.0, False, False), 256, 2, 1),   # chain 2048: two accumulators
-    ((1024, 1024, 512, 1, False, False, False, False, 1.0, False, False), 256, 1, 4),   # 16 tiles on 74 slots: split 4, chain 128
+    ((1024, 1024, 512, 1, False, False, False, False, 1.0, False, False), 128, 2, 2),   # 16 wide tiles on 74 slots: 32 narrow ones, split 2
     ((256, 64, 256, 6, False, False, False, False, 0.125, False, False), 64, 2, 2),
     ((384, 192, 512, 1, False, True, False, True, 1.0, False, False), 128, 2, 4),
 ])
