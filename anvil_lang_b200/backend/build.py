@@ -50,7 +50,8 @@ def _stamp(paths) -> str:
 
 
 def runtime_sources():
-    return [os.path.join(CSRC, "anvil_rt.cu"), os.path.join(CSRC, "anvil_colsum_static.cu"), os.path.join(CSRC, "anvil_rng.h"),
+    return [os.path.join(CSRC, "anvil_rt.cu"), os.path.join(CSRC, "anvil_colsum_static.cu"), os.path.join(CSRC, "anvil_selftest.cu"),
+            os.path.join(CSRC, "anvil_gemm_sm100.cuh"), os.path.join(CSRC, "anvil_rng.h"),
             os.path.join(INCLUDE, "anvil_cuda.h")]
 
 
@@ -139,6 +140,7 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_time_launch": (I, [P, P, I, I, c.POINTER(c.c_float)]),
         "anvil_rt_set_allreduce": (None, [P, P, P]), "anvil_rt_allreduce": (I, [P, Z, L]),
         "anvil_colsum_f32_static": (I, [P, L, L, P, P]),
+        "anvil_rt_selftest_wait": (I, [P, c.c_longlong, c.POINTER(U), c.POINTER(c.c_longlong)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

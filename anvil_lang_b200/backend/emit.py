@@ -43,12 +43,16 @@ def ctype(dt) -> str:
 
 
 def flit(v: float) -> str:
-    if math.isnan(v):
+    """An f32 literal: the shortest decimal text that round-trips the double, with an `f` suffix, or the CUDA names
+    of the special values."""
+    v = float(v)
+    if v != v:
         return "CUDART_NAN_F"
-    if math.isinf(v):
+    if v in (math.inf, -math.inf):
         return "CUDART_INF_F" if v > 0 else "(-CUDART_INF_F)"
-    r = repr(float(v))
-    return f"{r}f" if ("e" in r or "." in r) else f"{r}.0f"
+    text = repr(v)
+    needs_point = not any(ch in text for ch in ".e")
+    return text + (".0f" if needs_point else "f")
 
 
 def c_string(s: str) -> str:
@@ -242,56 +246,50 @@ class Scope:
             return f"{q}.{'xyzw'[lane % 4]}"
         return f"{p}[{self.affine(e.off, lane)}]"
 
+    # Scalar operators as tables: `{a}` / `{b}` are the operand texts, `{fa}` the operand as a float. The semantics
+    # are the interpreter's (anvil/interp.py:575-632): comparisons and logic give 0.0 / 1.0, integer arithmetic wraps,
+    # max / min propagate nan, floor division and modulo follow Python, a zero integer divisor counts as 1.
+    UNARY_ANY = {"detach": "{a}", "neg": "(-({a}))", "not": "(({a}) == 0 ? 1.0f : 0.0f)", "f32": "(float)({a})"}
+    UNARY_BY_TYPE = {            # op -> (text for an i32 operand, text for an f32 operand)
+        "abs": ("abs({a})", "fabsf({a})"), "i32": ("{a}", "anvil::f2i({a})"),
+        "sign": ("anvil::isign({a})", "anvil::fsign({a})"),
+        "floor": ("{a}", "floorf({a})"), "ceil": ("{a}", "ceilf({a})"), "round": ("{a}", "rintf({a})"),
+    }
+    UNARY_FLOAT = {"rsqrt": "(1.0f / sqrtf({fa}))", "recip": "(1.0f / ({fa}))", "sigmoid": "anvil::sigmoid({fa})",
+                   "exp": "expf({fa})", "log": "logf({fa})", "sqrt": "sqrtf({fa})", "tanh": "tanhf({fa})",
+                   "sin": "sinf({fa})", "cos": "cosf({fa})"}
+    COMPARE = {"lt": "<", "le": "<=", "gt": ">", "ge": ">=", "eq": "==", "ne": "!="}
+    LOGIC = {"and": "&&", "or": "||"}
+    BINARY_I32 = {"add": "(int)((uint32_t)({a}) + (uint32_t)({b}))", "sub": "(int)((uint32_t)({a}) - (uint32_t)({b}))",
+                  "mul": "(int)((uint32_t)({a}) * (uint32_t)({b}))", "idiv": "anvil::idiv({a}, {b})",
+                  "mod": "anvil::imod({a}, {b})", "max": "anvil::imax({a}, {b})", "min": "anvil::imin({a}, {b})"}
+    BINARY_F32 = {"add": "(({a}) + ({b}))", "sub": "(({a}) - ({b}))", "mul": "(({a}) * ({b}))", "div": "(({a}) / ({b}))",
+                  "max": "anvil::fmax_nan({a}, {b})", "min": "anvil::fmin_nan({a}, {b})", "pow": "powf({a}, {b})",
+                  "idiv": "floorf(({a}) / ({b}))", "mod": "anvil::fmod_py({a}, {b})"}
+
     def unary(self, e: kir.E, lane) -> str:
-        op, x = e.op, e.a[0]
-        isint = x.dt == I32
-        a = self.ex(x, lane)
-        if op == "detach":
-            return a
-        if op == "neg":
-            return f"(-({a}))"
-        if op == "abs":
-            return f"abs({a})" if isint else f"fabsf({a})"
-        if op == "not":
-            return f"(({a}) == 0 ? 1.0f : 0.0f)"
-        if op == "f32":
-            return f"(float)({a})"
-        if op == "i32":
-            return a if isint else f"anvil::f2i({a})"
-        if op == "sign":
-            return f"anvil::isign({a})" if isint else f"anvil::fsign({a})"
-        if op in ("floor", "ceil", "round"):
-            return a if isint else {"floor": "floorf", "ceil": "ceilf", "round": "rintf"}[op] + f"({a})"
-        fa = f"(float)({a})" if isint else a
-        if op == "rsqrt":
-            return f"(1.0f / sqrtf({fa}))"
-        if op == "recip":
-            return f"(1.0f / ({fa}))"
-        if op == "sigmoid":
-            return f"anvil::sigmoid({fa})"
-        return {"exp": "expf", "log": "logf", "sqrt": "sqrtf", "tanh": "tanhf", "sin": "sinf", "cos": "cosf"}[op] + f"({fa})"
+        operand = e.a[0]
+        a = self.ex(operand, lane)
+        integer = operand.dt == I32
+        if e.op in self.UNARY_ANY:
+            return self.UNARY_ANY[e.op].format(a=a)
+        if e.op in self.UNARY_BY_TYPE:
+            return self.UNARY_BY_TYPE[e.op][0 if integer else 1].format(a=a)
+        return self.UNARY_FLOAT[e.op].format(fa=f"(float)({a})" if integer else a)
 
     def binary(self, e: kir.E, lane) -> str:
-        op, x, y = e.op, e.a[0], e.a[1]
-        if op in kir.COMPARISONS or op in ("and", "or"):
-            a, b = self.ex(x, lane), self.ex(y, lane)
-            if op in ("and", "or"):
-                return f"((({a}) != 0 {'&&' if op == 'and' else '||'} ({b}) != 0) ? 1.0f : 0.0f)"
-            sym = {"lt": "<", "le": "<=", "gt": ">", "ge": ">=", "eq": "==", "ne": "!="}[op]
-            if x.dt != y.dt:
-                a, b = f"(float)({a})", f"(float)({b})"
-            return f"(({a}) {sym} ({b}) ? 1.0f : 0.0f)"
+        lhs, rhs = e.a
+        if e.op in self.LOGIC:
+            return f"((({self.ex(lhs, lane)}) != 0 {self.LOGIC[e.op]} ({self.ex(rhs, lane)}) != 0) ? 1.0f : 0.0f)"
+        if e.op in self.COMPARE:
+            if lhs.dt == rhs.dt:                     # same type: compared as they are; mixed: both as floats
+                a, b = self.ex(lhs, lane), self.ex(rhs, lane)
+            else:
+                a, b = self.cast(lhs, F32, lane), self.cast(rhs, F32, lane)
+            return f"(({a}) {self.COMPARE[e.op]} ({b}) ? 1.0f : 0.0f)"
         if e.dt == I32:
-            a, b = self.ex(x, lane), self.ex(y, lane)
-            if op in ("add", "sub", "mul"):
-                sym = {"add": "+", "sub": "-", "mul": "*"}[op]
-                return f"(int)((uint32_t)({a}) {sym} (uint32_t)({b}))"
-            return {"idiv": "anvil::idiv", "mod": "anvil::imod", "max": "anvil::imax", "min": "anvil::imin"}[op] + f"({a}, {b})"
-        a, b = self.cast(x, F32, lane), self.cast(y, F32, lane)
-        if op in ("add", "sub", "mul", "div"):
-            return f"(({a}) {dict(add='+', sub='-', mul='*', div='/')[op]} ({b}))"
-        return {"max": f"anvil::fmax_nan({a}, {b})", "min": f"anvil::fmin_nan({a}, {b})", "pow": f"powf({a}, {b})",
-                "idiv": f"floorf(({a}) / ({b}))", "mod": f"anvil::fmod_py({a}, {b})"}[op]
+            return self.BINARY_I32[e.op].format(a=self.ex(lhs, lane), b=self.ex(rhs, lane))
+        return self.BINARY_F32[e.op].format(a=self.cast(lhs, F32, lane), b=self.cast(rhs, F32, lane))
 
     # ---- statements (anvil/backend/cuda.py:249-264)
     def statements(self):
@@ -894,7 +892,8 @@ class KernelGen:
             S = max(1, min(296 // (tiles * NB), K // 128, 32))
         AK, BNC = ("true" if c.a_kcontig else "false"), ("true" if c.b_ncontig else "false")
         fn = f"G{k.id}"
-        if use_tensor_cores() and K % 4 == 0 and c.kvars[-1].extent % 4 == 0 and M >= 96 and N >= 64 and K >= 64:
+        if use_tensor_cores() and K % 4 == 0 and c.kvars[-1].extent % 4 == 0 and M >= 96 and N >= 64 and K >= 64 \
+                and c.flops >= tc_min_flops():
             return self.gen_gemm_tc(base, c, fn, fa, fb, fe, S)
         src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (CUDA-core tiles, split {S})"),
                f"struct {fn} {{", "    char *__restrict__ A;",
@@ -1048,6 +1047,14 @@ def use_row_groups() -> bool:
 def use_tensor_cores() -> bool:
     import os
     return os.environ.get("ANVIL_B200_TC", "1") != "0"
+
+
+def tc_min_flops() -> int:
+    """Products below this many FLOPs stay on the CUDA-core template: exact f32 products added in k order, no
+    3xTF32 split, and nothing to gain from the tensor pipe at that size (a launch costs more than the arithmetic).
+    ANVIL_B200_TC_MIN_MFLOP overrides the default of 128 MFLOP."""
+    import os
+    return int(float(os.environ.get("ANVIL_B200_TC_MIN_MFLOP", "128")) * 1e6)
 
 
 def tc_variant(a_kcontig: bool, M: int, N: int, K: int, nstores: int = 1) -> str:
@@ -1352,15 +1359,16 @@ class ProgramGen:
                                     + "\n".join(body) + "\n}")
         return idx
 
+    MAX_FAULT_CODES = 254
+
     def fault(self, message: str) -> int:
-        if message in self.faults:
-            return self.faults.index(message) + 1
-        if len(self.faults) >= 254:
+        """The code (1-based index into the program's message table) a kernel records for this bounds fault. The
+        fault word holds one byte of code: once the table is full, further messages share a generic entry."""
+        if message not in self.faults and len(self.faults) >= self.MAX_FAULT_CODES:
             message = "index out of bounds"
-            if message in self.faults:
-                return self.faults.index(message) + 1
-        self.faults.append(message)
-        return len(self.faults)
+        if message not in self.faults:
+            self.faults.append(message)
+        return 1 + self.faults.index(message)
 
     def need_scratch(self, nbytes: int):
         self.scratch_bytes = max(self.scratch_bytes, nbytes)
@@ -1537,12 +1545,14 @@ class ProgramGen:
         out.append(f"{ind}    RT(anvil_rt_set_i32(rt, {c}, (int32_t){lo}));")
         tail = [f"RT(anvil_rt_add_i32(rt, {c}, {st.step}));", "RT(anvil_rt_stream_commit(rt));"]
         if body_writes_counter or has_continue:
-            out.append(f"{ind}    for (long {i} = {lo}; {i} < {hi}; ) {{")
+            # The advance sits in the for statement's third clause, so a `continue` in the body reaches it
+            # (anvil/backend/cuda.py:445 does the same); a failing runtime call there ends the loop through `bad`.
+            bad = self.label("bad")
+            out.append(f"{ind}    int {bad} = 0;")
+            out.append(f"{ind}    for (long {i} = {lo}; {i} < {hi}; {i} = anvil_b200_advance(rt, {c}, {st.step}, &{bad})) {{")
             out += self.block(st.body, ind + "        ", True)
-            out.append(f"{ind}        RT(anvil_rt_add_i32(rt, {c}, {st.step}));")
-            out += self.read_scalar(st.counter, i + "_", ind + "        ")
-            out.append(f"{ind}        {i} = {i}_;")
             out.append(f"{ind}    }}")
+            out.append(f"{ind}    if ({bad}) return 1;")
         else:
             is_hot = st is self.hot and not any(isinstance(s, kir.Break) for b in kir.walk_blocks(st.body) for s in b.stmts)
             body = self.block(st.body, ind + "        ", True, tail)
@@ -1650,7 +1660,12 @@ class ProgramGen:
         out = [f"// Generated by anvil-b200 from {self.prog.name}: sm_100a kernels over one device arena.",
                "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
                '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', '#include "anvil_gemm_sm100.cuh"', "",
-               "#define RT(call) do { if ((call) != 0) return 1; } while (0)", ""]
+               "#define RT(call) do { if ((call) != 0) return 1; } while (0)", "",
+               "// advances a loop counter that lives in the arena and returns its new value; on a failure the loop ends",
+               "static long anvil_b200_advance(anvil_rt *rt, unsigned long off, int step, int *bad) {",
+               "    int32_t v = 0;",
+               "    if (anvil_rt_add_i32(rt, off, step) != 0 || anvil_rt_read_i32(rt, off, &v) != 0) { *bad = 1; return 0x7fffffffffffffffL; }",
+               "    return (long)v;", "}", ""]
         out += self.tables + [""]
         # --profile: one row per launch unit, "name label strategy" like the native back end's "name label location"
         names = [f"{k.name:<6} {k.label[:34]:<34} {note}" for k, note in zip(self.kernels, self.kernel_notes)]
@@ -1706,11 +1721,13 @@ class ProgramGen:
                     "    if (!rt) return 1;", f"    anvil_rt_seed(rt, {self.seed}u);"]
             for b in externs:
                 if b.kind == "input":
-                    out.append(f"    if (anvil_{b.name}) RT(anvil_rt_h2d_async(rt, {self.off(b)}, anvil_{b.name}, {max(b.nbytes, 4)}UL));")
+                    if b.nbytes:                     # an empty array has nothing to copy (its host pointer may be dangling)
+                        out.append(f"    if (anvil_{b.name}) RT(anvil_rt_h2d_async(rt, {self.off(b)}, anvil_{b.name}, {b.nbytes}UL));")
             out.append("    RT(anvil_b200_main(rt, 0));")
             for b in externs:
                 if b.kind == "output":
-                    out.append(f"    if (anvil_{b.name}) RT(anvil_rt_d2h_async(rt, anvil_{b.name}, {self.off(b)}, {max(b.nbytes, 4)}UL));")
+                    if b.nbytes:
+                        out.append(f"    if (anvil_{b.name}) RT(anvil_rt_d2h_async(rt, anvil_{b.name}, {self.off(b)}, {b.nbytes}UL));")
             out += ["    return anvil_rt_sync(rt);", "}"]
         return "\n".join(out) + "\n"
 

@@ -63,7 +63,8 @@ float *g_partials_addr[MAX_DEVICES];      // device address of g_colsum_partials
 }  // namespace
 
 extern "C" int anvil_colsum_f32_static(const float *x, long rows, long cols, float *out, void *cuda_stream) {
-    if (rows < 0 || cols < 0 || (rows > 0 && cols > 0 && (!x || !out))) {
+    // `out` is written whenever there is a column (zeros when there are no rows); `x` is read whenever there is an element
+    if (rows < 0 || cols < 0 || (cols > 0 && !out) || (rows > 0 && cols > 0 && !x)) {
         fprintf(stderr, "anvil: anvil_colsum_f32_static: bad arguments\n");
         return 1;
     }

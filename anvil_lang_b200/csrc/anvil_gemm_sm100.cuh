@@ -38,12 +38,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-// Optional phase stamps for timing studies: a translation unit may define ANVIL_TC_TRACE(slot) before
-// including this header; by default it expands to nothing.
-#ifndef ANVIL_TC_TRACE
-#define ANVIL_TC_TRACE(slot)
-#endif
-
 namespace anvil {
 namespace tc {
 
@@ -65,15 +59,16 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Bounded wait: false if the phase did not complete within ~2^31 clocks.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: false if the phase did not complete within `limit` clocks (by default ~2^31, about a second).
+constexpr long long WAIT_CLOCKS = 1LL << 31;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit = WAIT_CLOCKS) {
     const long long t0 = clock64();
     while (true) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
-        if (clock64() - t0 > (1LL << 31)) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 
@@ -729,7 +724,6 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
     const int nb0 = n0 + (int)rank * BH;                                         // this CTA's B rows
     const int k_begin = sp * KCH, k_end = min(K, k_begin + KCH);
     const int nkb = k_end > k_begin ? (k_end - k_begin + BK - 1) / BK : 0;
-    if (t == 0) { ANVIL_TC_TRACE(0); }
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFF);               // full[3], empty[3], accum
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + BAR_OFF + 64);
@@ -754,7 +748,6 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
     cluster_sync();                                                              // both CTAs' barriers and TMEM exist
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    if (t == 0) { ANVIL_TC_TRACE(1); }
 
     if (warp < MMA_WARP) {
         // ---------------------------------------------------------------- converters
@@ -814,7 +807,6 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             const int s = kb % NST;
             const uint32_t ph = (kb / NST) & 1;
             if (!mbar_wait_cluster(full(s), ph)) { *failed = 1; break; }
-            if (kb == 0) { ANVIL_TC_TRACE(2); }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
 #pragma unroll
@@ -828,14 +820,12 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             mma_commit_pair(empty(s));
         }
         mma_commit_pair(accum);
-        ANVIL_TC_TRACE(3);
     }
 
     // ---------------------------------------------------------------- epilogue: 128 rows x BN columns per CTA
     if (warp < MMA_WARP) {
         const bool ok = nkb == 0 || (!*failed && mbar_wait(accum, 0));
         if (!ok) *failed = 1;
-        if (t == 0) { ANVIL_TC_TRACE(4); }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         float *stage_f = reinterpret_cast<float *>(smem) + warp * (32 * 33);
         const int q = warp & 3;
@@ -864,7 +854,6 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
             }
             __syncwarp();
         }
-        if (t == 0) { ANVIL_TC_TRACE(5); }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -873,7 +862,6 @@ __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(2 * BN)) : "memory");
     }
-    if (t == 0) { ANVIL_TC_TRACE(6); }
     if (t == 0 && *failed) atomicExch(status, TIMEOUT);
 }
 
@@ -956,7 +944,6 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         mbar_init(alldone, 1);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        ANVIL_TC_TRACE(0);
     }
     if (warp == PP_MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
@@ -967,7 +954,6 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
     cluster_sync();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    if (t == 0) { ANVIL_TC_TRACE(1); }
 
     // One 32-row x 32-column piece of an accumulator buffer: tensor memory -> registers -> transposed through
     // `stage_f` (32 x 33 floats of this warp) -> the statements, eight rows at a time: first everything the
@@ -1142,7 +1128,6 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
                 for (int kb = 0; kb < it.nkb; kb++, n++) {
                     const int s = (int)(n % NST);
                     if (!mbar_wait_cluster(full(s), (uint32_t)(n / NST) & 1u)) { *failed = 1; break; }
-                    if (n == 0) { ANVIL_TC_TRACE(2); }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
 #pragma unroll
@@ -1164,7 +1149,6 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
                 mma_commit_pair(tfull(buf));
             }
             mma_commit_pair(alldone);                            // a barrier of its own: tfull's parity alone cannot tell the last use from an earlier one
-            ANVIL_TC_TRACE(3);
         }
     } else {
         // ---------------------------------------------------------------- epilogue warps
@@ -1200,7 +1184,6 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
                     drain(it, acc, half * CPW + cc, stage_f, cc == CPW - 1 ? buf : -1, tempty_leader0);
             }
         }
-        if (e == 0 && lane == 0) { ANVIL_TC_TRACE(5); }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -1209,7 +1192,6 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
-    if (t == 0) { ANVIL_TC_TRACE(6); }
     if (t == 0 && *failed) atomicExch(status, TIMEOUT);
 }
 

@@ -102,6 +102,7 @@ extern "C" void anvil_rt_destroy(anvil_rt *rt) {
     for (auto &g : rt->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     if (rt->arena) cudaFree(rt->arena);
     if (rt->ev0) { cudaEventDestroy(rt->ev0); cudaEventDestroy(rt->ev1); }
+    if (rt->pe0) { cudaEventDestroy(rt->pe0); cudaEventDestroy(rt->pe1); }
     if (rt->stream && rt->own_stream) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -159,7 +160,7 @@ extern "C" int anvil_rt_h2d_async(anvil_rt *rt, size_t off, const void *src, siz
 // argument of anvil.function): waits for the producer first — its stream when the interface names one
 // (`producer_stream` != 0), the whole device otherwise — then copies on the program's stream.
 extern "C" int anvil_rt_d2d_async(anvil_rt *rt, size_t off, const void *src_device, size_t bytes, void *producer_stream) {
-    if (off + bytes > rt->arena_bytes) return fail(rt, "anvil: copy outside the arena");
+    if (in_range(rt, off, bytes)) return 1;
     if (producer_stream) CK(rt, cudaStreamSynchronize((cudaStream_t)producer_stream));
     else CK(rt, cudaDeviceSynchronize());
     CK(rt, cudaMemcpyAsync(rt->arena + off, src_device, bytes, cudaMemcpyDeviceToDevice, rt->stream));
@@ -437,7 +438,9 @@ extern "C" int anvil_rt_input(anvil_rt *rt, size_t off, int *eof) {
 
 // n values from byte `offset` of a NumPy (or safetensors, kind + 16) file converted to 32 bits;
 // kinds: 0 f32, 1 f64, 2 f16, 3 i32, 4 i64, 5 u8, 6 i8, 7 u16, 8 i16 (anvil_host.h:189-220).
-extern "C" int anvil_rt_load_npy(anvil_rt *rt, const char *path, size_t off, long n, long offset, int kind, int size) {
+extern "C" int anvil_rt_load_npy(anvil_rt *rt, const char *path0, size_t off, long n, long offset, int kind, int size) {
+    const std::string path_s = data_path(path0);          // ANVIL_DATA relocates these files too (anvil_host.h:199)
+    const char *path = path_s.c_str();
     FILE *f = fopen(path, "rb");
     if (!f) return fail(rt, "anvil: cannot open data file %s", path);
     fseek(f, offset, SEEK_SET);

@@ -54,6 +54,32 @@ def _identity(domain) -> Affine:
     return Affine(0, list(zip(domain, strides)))
 
 
+def _require_mean_loss(kernels, loss_root):
+    """Gradients are summed over ranks and scaled by 1/G, which equals the global-batch gradient only when the loss
+    is a MEAN over the samples: the kernel that writes it must be a sum whose constant factor is 1 / (reduced elements)
+    (`sum_i -1/n * out[i, y[i]]`, the form the front end gives `mean` and `cross_entropy`). A summed loss would get
+    gradients G times too small, so it is refused."""
+    from .backend.contraction import _factors
+    writers = [k for k in kernels if any(s.buf.root is loss_root for s in k.stores)]
+    if not writers:
+        raise ShardError("the loss is not written by a kernel of the step")
+    k = writers[-1]
+    if k.red is None or k.red.op != "sum":
+        raise ShardError(f"the loss ({k.name}) is not a sum over the batch")
+    fs: list = []
+    _factors(k.red.body, fs)
+    c = 1.0
+    for f in fs:
+        if f.k == "const":
+            c *= float(f.val)
+        elif f.k == "un" and f.op == "neg" and f.a[0].k == "const":
+            c *= -float(f.a[0].val)
+    n = k.red_numel()
+    if abs(abs(c) * n - 1.0) > 1e-4:
+        raise ShardError(f"the loss ({k.name}) is not a mean: factor {c!r} over {n} elements; data-parallel gradient "
+                         f"scaling needs a mean loss")
+
+
 def shard(prog: kir.Program, world: int) -> kir.Program:
     """Rewrites `prog` (compiled for the local batch) in place for a run over `world` ranks. The
     result is the same for every rank: the rank is a run-time value in the 0-d tensor
@@ -174,6 +200,16 @@ def shard(prog: kir.Program, world: int) -> kir.Program:
         ur = {b.id for b in u.reads()}
         for k in kernels[upos + 1:]:
             if is_update[k.id]:
+                # a later update with a reduction has its gradient half hoisted in front of the all-reduce: that
+                # half must not read what this update writes (it would see the value from before the update)
+                if k.red is not None:
+                    red_reads = {n.buf.root.id for n in k.red.body.walk() if n.k == "load"}
+                    for n in k.red.body.walk():
+                        if n.k in ("load", "index"):
+                            for a in [n.off] + list(kir._nested(n.off)):
+                                red_reads |= {g.buf.root.id for g, _ in a.gathers()} | {s_.buf.root.id for s_, _ in a.scalars()}
+                    if uw & red_reads:
+                        raise ShardError(f"the gradient of {k.name} reads what the earlier update {u.name} writes")
                 continue
             if uw & {b.id for b in k.reads()} or uw & {b.id for b in k.writes()} \
                     or (ur - set(exchanged) - grad_ids) & {b.id for b in k.writes()}:
@@ -182,8 +218,11 @@ def shard(prog: kir.Program, world: int) -> kir.Program:
     bucket = grads + list(exchanged.values())
     tail = []
     loss = [b for b in prog.buffers if b.name == "loss" and b.root.id in written_first]
+    if not loss:
+        raise ShardError("no `loss` tensor is computed by the step: the 1/G scaling of the gradients assumes a mean loss")
     if loss:
         lb = loss[-1].root
+        _require_mean_loss(first, lb)
         bucket.append(lb)
         zero = Affine(0)
         tail.append(Kernel(next(ids), "loss_mean", "mean over ranks", [],

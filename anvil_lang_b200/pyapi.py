@@ -52,35 +52,50 @@ class DeviceArray:
         self.stream = int(st) if isinstance(st, int) and st > 2 else 0      # 1 / 2: the default streams
 
 
+_TENSOR_KINDS = {"f": (np.float32, kir.F32), "i": (np.int32, kir.I32), "u": (np.int32, kir.I32), "b": (np.int32, kir.I32)}
+
+
+def _constant_text(v) -> str:
+    """How a Python scalar argument is spelled in the function's source: it is a compile-time constant and part
+    of the signature (anvil/pyapi.py:216-221)."""
+    if v is True or v is False:
+        return "true" if v else "false"
+    if isinstance(v, str):
+        return '"' + v + '"'
+    if isinstance(v, float) and v != v:
+        return "nan"
+    if isinstance(v, float) and v in (float("inf"), float("-inf")):
+        return "inf" if v > 0 else "-inf"
+    return repr(v)
+
+
+def _host_tensor(a):
+    arr = np.asarray(a)
+    try:
+        np_type, dtype = _TENSOR_KINDS[arr.dtype.kind]
+    except KeyError:
+        raise TypeError(f"anvil: cannot pass an array of {arr.dtype} (use floats or integers)") from None
+    return np.ascontiguousarray(arr, dtype=np_type), dtype
+
+
 def arguments(args):
-    """NumPy arrays (or DeviceArray) for the tensor arguments, and the signature that picks the compiled version."""
+    """Splits a call's arguments into tensors (NumPy arrays converted to f32 / i32, or `DeviceArray`s for objects that
+    already live on the GPU) and the signature `(("tensor", shape, dtype) | ("const", text), ...)` that selects the
+    compiled version — the same signature the reference computes (anvil/pyapi.py:212-234), so lowered programs
+    stored under it are found by either implementation."""
     tensors, sig = [], []
     for a in args:
         if hasattr(a, "__cuda_array_interface__"):
-            d = DeviceArray(a)
-            tensors.append(d)
-            sig.append(("tensor", d.shape, d.dtype))
+            t = DeviceArray(a)
+            shape, dtype = t.shape, t.dtype
+        elif isinstance(a, (bool, int, float, str)) and not isinstance(a, np.generic):
+            sig.append(("const", _constant_text(a)))
             continue
-        if isinstance(a, (bool, int, float, str)) and not isinstance(a, np.generic):
-            if isinstance(a, bool):
-                text = "true" if a else "false"
-            elif isinstance(a, str):
-                text = f'"{a}"'
-            elif isinstance(a, float) and not np.isfinite(a):
-                text = "inf" if a > 0 else ("-inf" if a < 0 else "nan")
-            else:
-                text = repr(a)
-            sig.append(("const", text))
-            continue
-        arr = np.asarray(a)
-        if arr.dtype.kind == "f":
-            arr, dtype = np.ascontiguousarray(arr, dtype=np.float32), kir.F32
-        elif arr.dtype.kind in "iub":
-            arr, dtype = np.ascontiguousarray(arr, dtype=np.int32), kir.I32
         else:
-            raise TypeError(f"anvil: cannot pass an array of {arr.dtype} (use floats or integers)")
-        tensors.append(arr)
-        sig.append(("tensor", tuple(int(d) for d in arr.shape), dtype))
+            t, dtype = _host_tensor(a)
+            shape = tuple(map(int, t.shape))
+        tensors.append(t)
+        sig.append(("tensor", shape, dtype))
     return tensors, tuple(sig)
 
 
@@ -201,34 +216,38 @@ class Compiled:
 
 
 class Function:
-    """An Anvil function callable from Python on a B200 (anvil/pyapi.py:46-94)."""
+    """An Anvil function callable from Python on a B200: the counterpart of the reference's `Function`
+    (anvil/pyapi.py:46-94) with `Compiled` swapped for the GPU dispatcher. One `Compiled` per signature is kept."""
 
     def __init__(self, source: str, name: str | None = None, seed: int = 0, device: int = 0):
-        if "\n" not in source and source.endswith(".anvil") and os.path.exists(source):
-            self.path = os.path.abspath(source)
-            with open(source, encoding="utf-8") as f:
-                source = f.read()
-        else:
-            self.path = os.path.join(os.getcwd(), "<python>.anvil")
-        self.source = source if source.endswith("\n") else source + "\n"
-        self.name = name
-        self.seed = seed
-        self.device = device
+        self.path, text = self._resolve(source)
+        self.source = text if text.endswith("\n") else text + "\n"
+        self.name, self.seed, self.device = name, seed, device
         self.versions: dict[tuple, Compiled] = {}
+
+    @staticmethod
+    def _resolve(source: str):
+        """(`path` the diagnostics name, program text): `source` is either the text itself or the path of a .anvil file."""
+        is_file = "\n" not in source and source.endswith(".anvil") and os.path.exists(source)
+        if not is_file:
+            return os.path.join(os.getcwd(), "<python>.anvil"), source
+        with open(source, encoding="utf-8") as f:
+            return os.path.abspath(source), f.read()
+
+    def lower_sig(self, sig) -> Compiled:
+        if sig not in self.versions:
+            lowered = lower(self.source, self.path, self.name, sig, seed=self.seed)
+            self.versions[sig] = Compiled(self.name, lowered, seed=self.seed, device=self.device)
+        return self.versions[sig]
+
+    def lower(self, *args) -> Compiled:
+        """The compiled version these arguments would run, without running it."""
+        _, sig = arguments(args)
+        return self.lower_sig(sig)
 
     def __call__(self, *args):
         tensors, sig = arguments(args)
         return self.lower_sig(sig).call(tensors)
-
-    def lower(self, *args) -> Compiled:
-        return self.lower_sig(arguments(args)[1])
-
-    def lower_sig(self, sig) -> Compiled:
-        fn = self.versions.get(sig)
-        if fn is None:
-            lo = lower(self.source, self.path, self.name, sig, seed=self.seed)
-            fn = self.versions[sig] = Compiled(self.name, lo, seed=self.seed, device=self.device)
-        return fn
 
 
 def function(source: str, name: str | None = None, seed: int = 0) -> Function:

@@ -175,6 +175,15 @@ typedef int (*anvil_allreduce_fn)(void *user, void *device_ptr, long count, void
 void anvil_rt_set_allreduce(anvil_rt *rt, anvil_allreduce_fn fn, void *user);
 int anvil_rt_allreduce(anvil_rt *rt, size_t off, long count);
 
+/* ---- the bounded wait of the tensor-core templates, exercised on purpose (no reference counterpart: the
+ * reference's kernels never wait on one another). Runs one tiny kernel that waits, with a limit of `limit_clocks`
+ * SM clocks (at most 2^31), on a barrier nothing arrives on; the kernel gives up when the limit runs out, records
+ * the time-out in the arena header's status word like a contraction kernel would, and returns. `*status_out`
+ * receives that word (0x7C05 after a time-out), `*waited_clocks` the clocks spent waiting. The status word stays
+ * set, so the next anvil_rt_check_faults reports "a kernel gave up waiting on a barrier"; clear it with
+ * anvil_rt_zero(rt, ANVIL_RT_STATUS_OFF, 4). Nothing traps and the context stays usable. */
+int anvil_rt_selftest_wait(anvil_rt *rt, long long limit_clocks, uint32_t *status_out, long long *waited_clocks);
+
 /* ---- column sums without allocation (no counterpart in the reference: its runtime allocates every
  * tensor with cudaMallocManaged and has no entry point a caller could use under a no-allocation rule).
  * out[j] = sum_i x[i * cols + j] for a row-major f32 matrix; x and out are device pointers supplied by

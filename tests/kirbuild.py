@@ -34,11 +34,14 @@ def binop(op, a, b):
 
 
 def contraction_program(M, N, K, batch=1, ta=False, tb=False, bias=False, relu_a=False, alpha=1.0,
-                        accumulate=False, relu_out=False):
-    """C[b, m, n] (=|+=) epi(alpha * sum_k A[b, m, k] * B[b, k, n]); ta/tb store the operand transposed."""
+                        accumulate=False, relu_out=False, extra=""):
+    """C[b, m, n] (=|+=) epi(alpha * sum_k A[b, m, k] * B[b, k, n]); ta/tb store the operand transposed.
+    extra = "adam_m": a second store  Mo = 0.9 * Mo + 0.1 * acc  (a weight gradient with the first Adam moment fused);
+    extra = "residual": the result is added to what C holds through a plain in-place statement  C = C + acc (+ bias)."""
     A = buf("A", (batch, K, M) if ta else (batch, M, K))
     B = buf("B", (batch, N, K) if tb else (batch, K, N))
     C = buf("C", (batch, M, N))
+    Mo = buf("Mo", (batch, M, N))
     bias_b = buf("bias", (N,))
     b_, m, n, k = var("b", batch), var("m", M), var("n", N), var("k", K)
     a_ld = load(A, [(b_, M * K), (k, M), (m, 1)] if ta else [(b_, M * K), (m, K), (k, 1)])
@@ -55,17 +58,35 @@ def contraction_program(M, N, K, batch=1, ta=False, tb=False, bias=False, relu_a
         val = binop("max", val, const(0.0))
     dom = ([b_] if batch > 1 else []) + [m, n]
     off = Affine(0, [(b_, M * N), (m, N), (n, 1)] if batch > 1 else [(m, N), (n, 1)])
+    if extra == "residual":
+        val = binop("add", E("load", F32, buf=C, off=off), val)
+    stmts = [Store(C, off, val, accumulate)]
+    if extra == "adam_m":
+        stmts.append(Store(Mo, off, binop("add", binop("mul", const(0.9), E("load", F32, buf=Mo, off=off)),
+                                          binop("mul", const(0.1), E("acc", F32)))))
     if batch == 1:                       # drop the batch var from operand offsets
         for e in body.walk():
             if e.k == "load":
                 e.off = Affine(e.off.const, [(t, c) for t, c in e.off.terms if t is not b_])
                 e._key = None
-    kern = Kernel(nid(), f"k{nid()}", "test contraction", dom, [Store(C, off, val, accumulate)], Reduction([k], "sum", body))
-    prog = kir.Program(kir.Block([KernelStmt(kern)]), [A, B, C, bias_b], "contraction test")
+    kern = Kernel(nid(), f"k{nid()}", "test contraction", dom, stmts, Reduction([k], "sum", body))
+    prog = kir.Program(kir.Block([KernelStmt(kern)]), [A, B, C, bias_b, Mo], "contraction test")
     return prog, kern, A, B, C, bias_b
 
 
-def contraction_reference(a, b, c0, bias, M, N, K, batch, ta, tb, use_bias, relu_a, alpha, accumulate, relu_out):
+def contraction_reference(a, b, c0, bias, M, N, K, batch, ta, tb, use_bias, relu_a, alpha, accumulate, relu_out, extra=""):
+    """float64 result of `contraction_program`'s kernel for C (the value `acc` takes is `contraction_acc`)."""
+    r = contraction_acc(a, b, M, N, K, batch, ta, tb, relu_a, alpha)
+    if use_bias:
+        r = r + bias.astype(np.float64)
+    if relu_out:
+        r = np.maximum(r, 0)
+    if accumulate or extra == "residual":
+        r = r + c0.astype(np.float64).reshape(batch, M, N)
+    return r
+
+
+def contraction_acc(a, b, M, N, K, batch, ta, tb, relu_a, alpha):
     a = a.astype(np.float64).reshape((batch, K, M) if ta else (batch, M, K))
     b = b.astype(np.float64).reshape((batch, N, K) if tb else (batch, K, N))
     if ta:
@@ -74,11 +95,4 @@ def contraction_reference(a, b, c0, bias, M, N, K, batch, ta, tb, use_bias, relu
         b = b.transpose(0, 2, 1)
     if relu_a:
         a = np.maximum(a, 0)
-    r = alpha * np.matmul(a, b)
-    if use_bias:
-        r = r + bias.astype(np.float64)
-    if relu_out:
-        r = np.maximum(r, 0)
-    if accumulate:
-        r = r + c0.astype(np.float64).reshape(batch, M, N)
-    return r
+    return alpha * np.matmul(a, b)

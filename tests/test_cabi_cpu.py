@@ -47,3 +47,16 @@ def test_function_library_exports_the_reference_abi():
     assert hasattr(lib, "anvil_entry")
     for b in lo.inputs + [o for o in lo.outputs if o is not None]:
         ctypes.c_void_p.in_dll(lib, f"anvil_{b.name}")        # raises if the slot is missing
+
+
+def test_static_column_sum_refuses_bad_arguments_without_launching():
+    """Status codes that are decided before any CUDA call: a missing output with columns to write (also when there
+    are no rows: the sums are then zeros and still stored), a missing input with elements to read, negative sizes."""
+    lib = build.load_runtime()
+    f = lib.anvil_colsum_f32_static
+    dummy = ctypes.c_void_p(0x1000)                           # never dereferenced: every call below is refused or empty
+    assert f(dummy, 0, 8, None, None) == 1                    # no rows, columns, no output
+    assert f(None, 4, 8, dummy, None) == 1                    # elements to read, no input
+    assert f(dummy, -1, 8, dummy, None) == 1
+    assert f(dummy, 4, -1, dummy, None) == 1
+    assert f(None, 4, 0, None, None) == 0                     # nothing to do

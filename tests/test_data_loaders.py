@@ -148,3 +148,36 @@ def test_input_reads_numbers_until_the_end_of_the_input():
     assert r.returncode == 0, r.stderr
     lines = r.stdout.split("\n")
     assert float(lines[0]) == 2.5 and float(lines[1]) == -7.0 and lines[2] == ""      # third read: end of input -> newline, exit 0
+
+
+@pytest.mark.gpu
+def test_device_npy_loader_honours_the_data_directory(tmp_path):
+    """`.npy` files are relocated by ANVIL_DATA like the other data files (reference anvil/backend/anvil_host.h:199):
+    the program names a directory that does not exist, the file is found in the data directory; f32, i64 and f16
+    payloads are converted to 32 bits."""
+    from anvil_lang_b200.program import DeviceProgram
+    d = str(tmp_path)
+    rng = np.random.default_rng(5)
+    cases = [("w.npy", rng.standard_normal((3, 5)).astype(np.float32), F32, 0, 4),
+             ("idx.npy", rng.integers(-1000, 1000, size=7).astype(np.int64), I32, 4, 8),
+             ("h.npy", rng.standard_normal(9).astype(np.float16), F32, 2, 2)]
+    bufs, calls = [], []
+    for name, arr, dt, kind, size in cases:
+        np.save(os.path.join(d, name), arr)
+        with open(os.path.join(d, name), "rb") as f:            # the payload starts after the header
+            f.seek(8)
+            hlen = int.from_bytes(f.read(2), "little")
+        b = Buffer(nid(), name[:-4], arr.shape, dt, "temp")
+        bufs.append((b, arr))
+        calls.append(RTCall("load_npy", {"buf": b, "path": os.path.join(d, "not_here", name), "offset": 10 + hlen,
+                                         "kind": kind, "size": size}))
+    prog = kir.Program(kir.Block(calls), [b for b, _ in bufs], "npy")
+    dp = DeviceProgram(prog, seed=0)
+    try:
+        code, _ = dp.run(capture=True)
+        assert code == 0, dp.error
+        for b, arr in bufs:
+            want = arr.reshape(-1).astype(np.int32 if b.dtype == I32 else np.float32)
+            assert np.array_equal(dp.read(b).reshape(-1), want), b.name
+    finally:
+        dp.close()

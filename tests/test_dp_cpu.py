@@ -67,3 +67,40 @@ def test_shard_structure():
     assert not any(st.buf.root.kind in ("param", "state") for k in before for st in k.stores)
     assert all(k.red is None for k in after)
     assert sum(b.nbytes for b in prog.bucket) == 4 * (784 * 1024 + 1024 + 1024 * 1024 + 1024 + 1024 * 10 + 10 + 1)
+
+
+def _dp_mlp():
+    return kir.load(os.path.join(GOLDEN, "dp_mlp.b16.kir.json.gz"))
+
+
+def test_a_summed_loss_is_refused():
+    """The 1/G scaling of the summed gradients is only right for a MEAN loss: with the loss's 1/n factor removed
+    (a batch sum) sharding must raise instead of training with gradients G times too small."""
+    from anvil_lang_b200.backend.analysis import hot_loop
+    prog = _dp_mlp()
+    hot = hot_loop(prog)
+    k = [s.kernel for s in hot.body.stmts if isinstance(s, kir.KernelStmt)
+         and any(st.buf.name == "loss" for st in s.kernel.stores)][-1]
+    consts = [n for n in k.red.body.walk() if n.k == "const"]
+    assert consts
+    for c in consts:
+        c.val, c._key = -1.0, None
+    with pytest.raises(dp.ShardError, match="not a mean"):
+        dp.shard(prog, 2)
+
+
+def test_a_gradient_that_reads_an_earlier_update_is_refused():
+    """Updates move behind the all-reduce while the gradient half of a later update stays in front of it: if that
+    gradient reads a parameter an earlier update wrote, it would see the stale value, so sharding must raise."""
+    from anvil_lang_b200.backend.analysis import hot_loop
+    from anvil_lang_b200.kir import F32, Affine, E
+    prog = _dp_mlp()
+    hot = hot_loop(prog)
+    ks = [s.kernel for s in hot.body.stmts if isinstance(s, kir.KernelStmt)]
+    upd = [k for k in ks if any(st.buf.root.kind == "param" for st in k.stores)]
+    assert len(upd) >= 2 and upd[-1].red is not None
+    earlier_param = [st.buf for st in upd[0].stores if st.buf.root.kind == "param"][0]
+    last = upd[-1]
+    last.red.body = E("bin", F32, op="mul", a=[last.red.body, E("load", F32, buf=earlier_param, off=Affine(0))])
+    with pytest.raises(dp.ShardError, match="reads what the earlier update"):
+        dp.shard(prog, 2)

@@ -88,3 +88,27 @@ def test_operand_prefetch_functors_exist_for_resident_pairs():
     src, _ = gen((512, 512, 512, 1, False, False, False, False, 1.0, False, False))
     assert "void a_touch(int m, int k, int bt)" in src and "void b_touch(int k, int n, int bt)" in src
     assert src.count("anvil::prefetch_l2(") >= 2
+
+
+def test_continue_in_a_for_loop_still_advances_the_counter():
+    """A `continue` inside a counted loop must reach the counter's advance (reference anvil/backend/cuda.py:445 puts
+    it in the for statement's third clause); otherwise the host would launch the body for ever."""
+    import os as _os
+    from anvil_lang_b200 import kir
+    from util import GOLDEN
+    prog = kir.load(_os.path.join(GOLDEN, "control_flow.kir.json.gz"))
+    src = emit.generate(prog, 0)[0]
+    loops = [m for m in re.finditer(r"for \(long (i\d+) = lo\d+; i\d+ < hi\d+; ([^)]*\)?)\) \{", src)]
+    with_continue = []
+    for m in loops:
+        depth, j = 1, m.end()
+        while depth:
+            depth += {"{": 1, "}": -1}.get(src[j], 0)
+            j += 1
+        body = src[m.end():j]
+        if re.search(r"\bcontinue;", body):
+            with_continue.append((m, body))
+    assert with_continue, "the fixture has a `for` with `continue`"
+    for m, body in with_continue:
+        assert "anvil_b200_advance(rt," in m.group(0), m.group(0)       # the advance is the loop's third clause
+        assert "anvil_rt_add_i32" not in body.split("continue;")[-1]      # not at the bottom of the body

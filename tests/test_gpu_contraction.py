@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from anvil_lang_b200.program import DeviceProgram
-from kirbuild import contraction_program, contraction_reference
+from kirbuild import contraction_acc, contraction_program, contraction_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -31,14 +31,28 @@ CASES = [
 ]
 
 
+# Shapes of the full-size transformer step (M = batch x T = 16384, D = 512) that the list above does not reach, with
+# the epilogues they carry there. They run with the emitter's own choice and on the resident pairs.
+#   M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out, extra
+BIG_CASES = [
+    (512, 512, 16384, 1, True, False, False, False, 1.0, False, False, "adam_m"),     # dW of Wq/Wk/Wv/Wo: A read along m, split-k
+    (2048, 512, 16384, 1, True, False, False, False, 1.0, False, False, "adam_m"),    # dW of the MLP's second matrix
+    (512, 2048, 16384, 1, True, False, False, False, 1.0, False, False, "adam_m"),    # dW of the MLP's first matrix
+    (16384, 512, 512, 1, False, True, False, False, 1.0, True, False, ""),             # dX through W^T, `+=` into dh
+    (16384, 512, 512, 1, False, False, False, False, 1.0, False, False, "residual"),   # x = x + o @ Wo
+    (16384, 256, 512, 1, False, False, True, False, 1.0, False, False, ""),            # logits
+]
+
+
 def run_case(case, tc):
     """tc: True (the emitter's choice), "pp" (resident CTA pairs walking over the tiles), "pair" (two CTAs of a cluster on one 256-row tile, cta_group::2; shapes too
     small for it take the emitter's choice), "ts" (A tiles in tensor memory), "ss" (operands in shared memory, two CTAs
     per SM), "ss32" (operands in shared memory, one CTA per SM, 32-wide k blocks), False (CUDA cores)."""
-    M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out = case
+    M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out = case[:11]
+    extra = case[11] if len(case) > 11 else ""
     os.environ["ANVIL_B200_TC"] = {True: "1", False: "0"}.get(tc, tc)
     try:
-        prog, kern, A, B, C, bias_b = contraction_program(M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out)
+        prog, kern, A, B, C, bias_b = contraction_program(*case)
         dp = DeviceProgram(prog, graphs=False)
     finally:
         os.environ.pop("ANVIL_B200_TC", None)
@@ -48,13 +62,21 @@ def run_case(case, tc):
     b = rng.standard_normal(B.numel, dtype=np.float32)
     c0 = rng.standard_normal(C.numel, dtype=np.float32)
     bv = rng.standard_normal(N, dtype=np.float32)
-    dp.write(A, a); dp.write(B, b); dp.write(C, c0); dp.write(bias_b, bv)
+    Mo = [x for x in prog.buffers if x.name == "Mo"][0]
+    m0 = rng.standard_normal(Mo.numel, dtype=np.float32)
+    dp.write(A, a); dp.write(B, b); dp.write(C, c0); dp.write(bias_b, bv); dp.write(Mo, m0)
     dp.launch(kern)
     dp.check_faults()
     got = dp.read(C).astype(np.float64)
+    got_m = dp.read(Mo).astype(np.float64)
     dp.close()
-    want = contraction_reference(a, b, c0, bv, M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out)
+    want = contraction_reference(a, b, c0, bv, M, N, K, batch, ta, tb, bias, relu_a, alpha, accumulate, relu_out, extra)
     err = np.abs(got - want).max() / max(np.abs(want).max(), 1e-30)
+    if extra == "adam_m":                                  # the moment is linear in the product: same bar
+        want_m = 0.9 * m0.astype(np.float64).reshape(batch, M, N) + 0.1 * contraction_acc(a, b, M, N, K, batch, ta, tb, relu_a, alpha)
+        err = max(err, np.abs(got_m - want_m).max() / max(np.abs(want_m).max(), 1e-30))
+    else:
+        assert np.array_equal(got_m.reshape(-1), m0.astype(np.float64))      # untouched
     return err, note
 
 
@@ -76,3 +98,11 @@ def test_cuda_core_contraction(case):
 def test_large_shapes_take_the_tensor_core_template():
     _, note = run_case(CASES[1], tc=True)
     assert note.startswith("gemm tc")
+
+
+@pytest.mark.parametrize("variant", [True, "pp"])
+@pytest.mark.parametrize("case", BIG_CASES, ids=lambda c: "x".join(map(str, c[:3])) + ("_" + c[11] if c[11] else ""))
+def test_full_size_transformer_products(case, variant):
+    err, note = run_case(case, tc=variant)
+    assert note.startswith("gemm tc"), note
+    assert err < 3e-5, (err, note)
