@@ -1054,6 +1054,8 @@ def tc_min_flops() -> int:
     3xTF32 split, and nothing to gain from the tensor pipe at that size (a launch costs more than the arithmetic).
     ANVIL_B200_TC_MIN_MFLOP overrides the default of 128 MFLOP."""
     import os
+    if os.environ.get("ANVIL_B200_TC", "1") in ("pp", "pair", "ts", "ss", "ss32"):
+        return 0                                     # a template forced by name is taken at any size
     return int(float(os.environ.get("ANVIL_B200_TC_MIN_MFLOP", "128")) * 1e6)
 
 

@@ -96,8 +96,10 @@ def test_cuda_core_contraction(case):
 
 
 def test_large_shapes_take_the_tensor_core_template():
-    _, note = run_case(CASES[1], tc=True)
+    _, note = run_case(CASES[9], tc=True)               # 1024^3
     assert note.startswith("gemm tc")
+    _, note = run_case(CASES[1], tc=True)               # 33 MFLOP: below the tensor-core threshold
+    assert note.startswith("gemm simt")
 
 
 @pytest.mark.parametrize("variant", [True, "pp"])
