@@ -1,16 +1,28 @@
 """Loss trajectories of the BASELINE configurations on the device.
 
-Two comparisons, because ReLU / max-pool networks are not continuous in their rounding errors: when a
-pre-activation lands within an ulp of zero, two correct f32 implementations that sum in a different
-order put it on different sides of the kink, one mask element flips, and the trajectories separate
-for good. The reference interpreter itself, re-run with its parameters perturbed by one ulp, drifts
-from its own recorded trajectory by 5e-4 (C4, step 24) and 5e-3 (C3, step 68) — measured with the CPU
-oracle. So:
+The bar is 1e-3 relative over the first 100 steps against the reference interpreter's recorded losses
+(tests/golden/*.losses.json). Measured free-running on a B200, per configuration and per contraction path
+(default routing / every product on the exact-product CUDA-core template / every product on tensor cores):
 
-  * windowed: every 10 steps the device state is re-synchronised from the oracle running alongside;
-    inside each window every loss must match the oracle's to 1e-3 (the project's trajectory bar);
-  * free-running from the program's own initialisation, against the reference interpreter's recorded
-    losses (tests/golden/*.losses.json): the first 10 steps to 1e-3, all steps to 2e-2.
+    configuration           default            CUDA cores only      tensor cores only
+    c1_mlp_sgd              4.1e-7 (100 steps)  4.1e-7               4.1e-7
+    c5_transformer_small    1.6e-7              1.6e-7               2.3e-7
+    c4_cnn_sgd              1.21e-3 at step 49  9.5e-4 at step 39    1.21e-3 at step 49
+    c3_mlp_adam             4.9e-3 at step 68   5.3e-3 at step 68    4.9e-3 at step 68
+                            (first > 1e-3: 34)  (first > 1e-3: 45)
+
+C1 and the reduced transformer hold the bar with three orders of magnitude to spare and are asserted at 1e-3 over all
+100 steps. C3 and C4 leave it on EVERY path, including the one that multiplies in exact f32 and adds in k order, so
+the cause is not the 3xTF32 split: ReLU / max-pool networks are not continuous in their rounding errors (a
+pre-activation within an ulp of zero lands on different sides of the kink in two correct f32 implementations), and
+Adam's g / (sqrt(v) + 1e-8) turns the rounding noise of a near-cancelled gradient sum into a 1e-3 step. The CPU
+oracle re-run with its parameters perturbed by ONE ulp drifts from the interpreter's own recorded losses by 5e-4 at
+C4 step 24 and 5e-3 at C3 step 68 — the same size and the same step as the device. So for those two:
+
+  * windowed: every 10 steps the device state is re-synchronised from the oracle running alongside; inside each
+    window every loss must match the oracle's to 1e-3 — all four configurations;
+  * free-running: 1e-3 for as long as the exact-product path itself holds it (C4: 35 steps, C3: 30 steps), and a
+    bound just above the measured drift for the rest (C4 2e-3, C3 1e-2).
 """
 import io
 import json
@@ -34,6 +46,8 @@ CONFIGS = {
     "c4_cnn_sgd": (os.path.join(ROOT, "anvil_lang_b200", "programs", "c4_cnn_sgd.kir.json.gz"), 100, 30),
     "c5_transformer_small": (os.path.join(GOLDEN, "c5_transformer_small.traj.kir.json.gz"), 100, 50),
 }
+# free-running bars: (steps that must hold 1e-3, bound over all 100 steps) — see the table in the module docstring
+FREE_BARS = {"c1_mlp_sgd": (100, 1e-3), "c5_transformer_small": (100, 1e-3), "c4_cnn_sgd": (35, 2e-3), "c3_mlp_adam": (30, 1e-2)}
 
 
 def free_running(prog, steps):
@@ -58,8 +72,9 @@ def test_free_running_trajectory(cfg):
     want = json.load(open(os.path.join(GOLDEN, f"{cfg}.losses.json")))["losses"][:steps]
     got = free_running(kir.load(path), len(want))
     rel = np.abs(np.array(got) - np.array(want)) / np.abs(want)
-    assert rel[:10].max() <= 1e-3, rel[:10]
-    assert rel.max() <= 2e-2, (int(rel.argmax()), float(rel.max()))
+    tight_steps, bound = FREE_BARS[cfg]
+    assert rel[:tight_steps].max() <= 1e-3, (int(rel[:tight_steps].argmax()), float(rel[:tight_steps].max()))
+    assert rel.max() <= bound, (int(rel.argmax()), float(rel.max()))
 
 
 def test_full_size_c5_first_steps():
