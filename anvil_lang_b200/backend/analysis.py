@@ -142,21 +142,173 @@ def hot_loop(prog: kir.Program):
 
 class ArenaPlan:
     """Byte offsets of every root buffer inside the runtime's arena. The header comes first, then a
-    scratch region for split reductions, then the buffers."""
+    scratch region for split reductions, then the all-reduce bucket, then the region in which temporaries with
+    disjoint lifetimes share bytes, then every other buffer in memory of its own."""
 
     def __init__(self, offsets: dict, size: int, scratch_off: int, scratch_bytes: int):
         self.offsets = offsets
         self.size = size
         self.scratch_off = scratch_off
         self.scratch_bytes = scratch_bytes
+        self.shared: set = set()         # root ids whose bytes other tensors reuse once they are dead
+        self.unused: set = set()         # root ids nothing touches (a gradient a fused update keeps in registers)
+        self.shared_bytes = 0            # size of the shared region
+        self.unshared_bytes = 0          # what its tensors would take with memory of their own
+        self.spans: dict = {}            # root id -> (first, last) statement position of a shared tensor
 
     def off(self, b: kir.Buffer) -> int:
         return self.offsets[b.root.id]
 
+    @property
+    def clobbered(self) -> set:
+        """Root ids whose contents are not meaningful after the program has run."""
+        return self.shared | self.unused
 
-def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256) -> ArenaPlan:
-    """Every root buffer gets its own zero-initialised, 256-byte aligned region (the reference gives
-    each buffer its own zeroed allocation, anvil/backend/cuda.py:416-421)."""
+
+SHARED_KINDS = ("temp", "grad")
+FULL_WRITE_CALLS = ("nonzero", "input", "clock", "iota", "iota_once")
+MIN_SHARED_BYTES = 4096                  # smaller tensors keep their own memory: nothing to gain
+
+
+def covers(k: kir.Kernel, st: kir.Store) -> bool:
+    """Does this store write EVERY element of its tensor, each exactly once? (The reference's planner asks for
+    `domain extents == buffer shape` with the identity offset, anvil/backend/arena.py:46-57, which a collapsed loop nest
+    no longer satisfies; a bijection of the domain onto the tensor is what is actually needed.)"""
+    if st.accumulate or not st.offset.is_plain() or k.rand_base is not None:
+        return False
+    r = st.buf.root
+    if k.out_numel() != r.numel or r.numel == 0:
+        return False
+    bounds = st.offset.bounds()
+    return bounds == (0, r.numel - 1) and injective_over(st.offset, k.domain)
+
+
+class _Use:
+    __slots__ = ("pos", "chain", "write", "full")
+
+    def __init__(self, pos, chain, write, full):
+        self.pos, self.chain, self.write, self.full = pos, chain, write, full
+
+
+def _flatten(prog: kir.Program, fused_runs):
+    """Every use of every root buffer with its statement position and the loops / branches around it, and the
+    position ranges of the loops (the walk of anvil/backend/arena.py:36-98 over this IR). `fused_runs(kernels)` gives
+    index ranges of consecutive kernels that the emitter runs as ONE kernel: they share a position, so nothing
+    one of them reads can give its bytes to something another one writes."""
+    uses: dict = {}
+    loops: list = []
+    pos = 0
+
+    def note(b, chain, write=False, full=False):
+        if isinstance(b, kir.Buffer):
+            uses.setdefault(b.root.id, []).append(_Use(pos, chain, write, full))
+
+    def kernel_uses(k, chain):
+        full = {st.buf.root.id for st in k.stores if covers(k, st)}
+        for r in k.reads():
+            note(r, chain)
+        for r in k.writes():
+            note(r, chain, True, r.id in full)
+
+    def block(b: kir.Block, chain):
+        nonlocal pos
+        stmts = b.stmts
+        i = 0
+        while i < len(stmts):
+            st = stmts[i]
+            if isinstance(st, kir.KernelStmt):
+                j = i
+                while j < len(stmts) and isinstance(stmts[j], kir.KernelStmt):
+                    j += 1
+                run = [x.kernel for x in stmts[i:j]]
+                starts = dict(fused_runs(run)) if fused_runs else {}
+                q = 0
+                while q < len(run):
+                    pos += 1
+                    end = starts.get(q, q + 1)
+                    for k in run[q:end]:
+                        kernel_uses(k, chain)
+                    q = end
+                i = j
+                continue
+            stmt(st, chain)
+            i += 1
+
+    def stmt(st, chain):
+        nonlocal pos
+        pos += 1
+        if isinstance(st, kir.For):
+            start = pos
+            note(st.start, chain); note(st.stop, chain)
+            note(st.counter, chain, True)
+            block(st.body, chain + (("loop", id(st)),))
+            pos += 1
+            loops.append((start, pos))
+        elif isinstance(st, kir.While):
+            start = pos
+            inner = chain + (("loop", id(st)),)
+            block(st.cond_block, inner)
+            pos += 1
+            note(st.cond, inner)
+            block(st.body, inner)
+            pos += 1
+            loops.append((start, pos))
+        elif isinstance(st, kir.If):
+            note(st.cond, chain)
+            block(st.then, chain + (("then", id(st)),))
+            block(st.orelse, chain + (("else", id(st)),))
+            pos += 1
+        elif isinstance(st, kir.Print):
+            for it in st.items:
+                note(it.buf, chain)
+        elif isinstance(st, kir.Check):
+            for t, _ in st.value.scalars():
+                note(t.buf, chain)
+        elif isinstance(st, kir.RTCall):
+            target = st.args.get("buf")
+            for key, v in st.args.items():
+                for x in (v if isinstance(v, list) else [v]):
+                    if isinstance(x, kir.Buffer):
+                        is_target = x is target and st.name not in ("save", "save_npy", "show", "sleep", "shuffle")
+                        note(x, chain, is_target, is_target and st.name in FULL_WRITE_CALLS)
+                        if st.name in ("load", "shuffle"):
+                            note(x, chain, True, False)
+        elif isinstance(st, kir.AllReduce):
+            for b in st.bufs:
+                note(b, chain, True, False)
+    block(prog.main, ())
+    return uses, loops
+
+
+def _lifetime(us, loops):
+    """[first, last] position over which a tensor holds a value somebody still needs, or None when it has to keep
+    memory of its own: its first use must write all of it (nothing may rely on the initial zeros), and that write must
+    be certain to have run before every other use (anvil/backend/arena.py:101-118)."""
+    first = us[0].pos
+    at_first = [u for u in us if u.pos == first]
+    if any(not u.write for u in at_first) or not any(u.full for u in at_first):
+        return None
+    chain = at_first[0].chain
+    if any(u.chain[:len(chain)] != chain for u in us):
+        return None
+    lo, hi = first, us[-1].pos
+    changed = True
+    while changed:                                   # a lifetime that enters or leaves a loop covers the whole loop
+        changed = False
+        for a, b in loops:
+            if lo <= b and a <= hi and not (a <= lo and hi <= b) and (a < lo or b > hi):
+                lo, hi = min(lo, a), max(hi, b)
+                changed = True
+    return lo, hi
+
+
+def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256, share: bool = True, fused_runs=None,
+               keep=()) -> ArenaPlan:
+    """One arena for the whole program. Temporaries (`temp`, `grad`) whose first use writes all of them and whose
+    lifetimes do not overlap share bytes (first fit by decreasing size, ids break ties: the layout is the same every
+    run, like anvil/backend/arena.py:121-144); tensors nothing touches get no memory; every other root buffer
+    gets its own zero-initialised, 256-byte aligned region (the reference gives each its own zeroed allocation,
+    anvil/backend/cuda.py:416-421). `keep`: root ids that must not share (tensors the host reads or feeds)."""
     def up(n):
         return (n + ALIGN - 1) // ALIGN * ALIGN
     pos = up(header)
@@ -170,13 +322,51 @@ def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256) -> 
             offsets[r.id] = pos
             pos += up(max(r.nbytes, 16))
     bucket_bytes = pos - bucket_off
-    for r in prog.roots():
+    plan = ArenaPlan(offsets, 0, scratch_off, up(max(scratch_bytes, 4)))
+    plan.bucket_off, plan.bucket_bytes = bucket_off, bucket_bytes
+    uses, loops = _flatten(prog, fused_runs)
+    roots = prog.roots()
+    items = []
+    if share:
+        for r in roots:
+            if r.id in offsets or r.id in keep or r.kind not in SHARED_KINDS or r.nbytes < MIN_SHARED_BYTES or r.init is not None:
+                continue
+            us = uses.get(r.id)
+            if not us:
+                continue
+            span = _lifetime(us, loops)
+            if span is not None:
+                items.append((r, span, up(r.nbytes)))
+        items.sort(key=lambda it: (-it[2], it[1][0], it[0].id))
+        placed: list = []                            # (lo, hi, offset, size)
+        region = 0
+        for r, (lo, hi), n in items:
+            busy = sorted((off, off + sz) for l2, h2, off, sz in placed if l2 <= hi and lo <= h2)
+            off = 0
+            for s_, e_ in busy:
+                if off + n <= s_:
+                    break
+                off = max(off, e_)
+            placed.append((lo, hi, off, n))
+            offsets[r.id] = pos + off
+            plan.shared.add(r.id)
+            plan.spans[r.id] = (lo, hi)
+            region = max(region, off + n)
+        plan.shared_bytes = region
+        plan.unshared_bytes = sum(n for _, _, n in items)
+        shared_base = pos
+        pos += region
+    for r in roots:
         if r.id in offsets:
+            continue
+        if share and r.id not in uses and r.kind in SHARED_KINDS and r.init is None and r.id not in keep \
+                and up(max(r.nbytes, 16)) <= plan.shared_bytes:
+            offsets[r.id] = shared_base              # nothing reads or writes it: no bytes of its own
+            plan.unused.add(r.id)
             continue
         offsets[r.id] = pos
         pos += up(max(r.nbytes, 16))
-    plan = ArenaPlan(offsets, pos, scratch_off, up(max(scratch_bytes, 4)))
-    plan.bucket_off, plan.bucket_bytes = bucket_off, bucket_bytes
+    plan.size = pos
     return plan
 
 

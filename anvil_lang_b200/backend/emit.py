@@ -1250,7 +1250,7 @@ class ProgramGen:
         self.seed = seed & 0xFFFFFFFF
         self.faults: list[str] = []
         self.scratch_bytes = 4
-        self.plan = an.plan_arena(prog, 0)
+        self.plan = self.make_plan(0)
         self.kernel_index: dict[int, int] = {}
         self.kernels: list[kir.Kernel] = []
         self.kernel_src: list[str] = []
@@ -1277,6 +1277,18 @@ class ProgramGen:
             for r in k.reads():
                 self.readers.setdefault(r.id, set()).add(k.id)
         self.host_read = self._host_reads()
+
+    def make_plan(self, scratch_bytes: int):
+        """The arena plan: lifetime sharing unless ANVIL_B200_ARENA=unshared. Tensors the host reads (printed values,
+        loop conditions, checkpoints) or feeds (the step's inputs) keep their own memory, so they can be read between
+        steps; row kernels that will run as one fused kernel count as one statement."""
+        hot = an.hot_loop(self.prog)
+        keep = set(self._host_reads())
+        if hot is not None:
+            keep |= {b.root.id for b in an.input_producers(self.prog, hot)[1]}
+        runs = (lambda ks: rg.find_groups(ks)) if use_row_groups() else None
+        return an.plan_arena(self.prog, scratch_bytes, share=os_environ("ANVIL_B200_ARENA", "shared") != "unshared",
+                             fused_runs=runs, keep=keep)
 
     def _host_reads(self) -> set:
         """Root ids of tensors that something other than a kernel reads."""
@@ -1740,12 +1752,15 @@ def generate(prog: kir.Program, seed: int = 0):
     if os_environ("ANVIL_B200_DETERMINISTIC", "1") != "0":
         from .determinism import make_deterministic
         make_deterministic(prog)                     # colliding `+=` get a fixed order (idempotent)
+    if os_environ("ANVIL_B200_REFUSE", "1") != "0":
+        from .refuse import fuse_consumers
+        fuse_consumers(prog)                         # optimizer updates join the kernel that makes their gradient (idempotent)
     g = ProgramGen(prog, seed)
     src = g.generate()
     if g.scratch_bytes > g.plan.scratch_bytes:
         need = g.scratch_bytes
         g = ProgramGen(prog, seed)
-        g.plan = an.plan_arena(prog, need)
+        g.plan = g.make_plan(need)
         g.scratch_bytes = need
         src = g.generate()
     return src, g

@@ -36,7 +36,7 @@ from anvil_lang_b200.backend.analysis import hot_loop
 from anvil_lang_b200.program import DeviceProgram
 from oracle.kir_interp import Oracle
 from test_gpu_kernel_parity import run_to_loop
-from util import GOLDEN, ROOT
+from util import GOLDEN, ROOT, device_program
 
 pytestmark = pytest.mark.gpu
 
@@ -99,7 +99,7 @@ def test_windowed_trajectory(cfg):
     for st in hot.body.stmts:
         if isinstance(st, kir.KernelStmt):
             loop_written |= {b.id for b in st.kernel.writes()}
-    dp = DeviceProgram(prog, seed=0)
+    dp = device_program(prog, unshared_arena=True, seed=0)       # every tensor is re-written from the oracle: none may alias
     dp.rtlib.anvil_rt_capture(dp.rt, 1)
     try:
         dp.prologue()

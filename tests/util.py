@@ -88,3 +88,15 @@ def check_arrays(read, prog, arrays, rel=1e-4, skip=()):
         if not ok:
             bad.append(f"{b.name}#{b.id}{list(b.shape)}: {why}")
     return bad
+
+
+def device_program(prog, unshared_arena=False, **kw):
+    """A DeviceProgram; `unshared_arena` builds it with every tensor in memory of its own (ANVIL_B200_ARENA=unshared),
+    so that temporaries can still be read after the run (by default dead temporaries give their bytes to later ones)."""
+    from anvil_lang_b200.program import DeviceProgram
+    if unshared_arena:
+        os.environ["ANVIL_B200_ARENA"] = "unshared"
+    try:
+        return DeviceProgram(prog, **kw)
+    finally:
+        os.environ.pop("ANVIL_B200_ARENA", None)
