@@ -213,9 +213,89 @@ def do_functions():
             print(name, "small" if small else "full", sig)
 
 
+def reference_test_programs(reference: str):
+    """The programs of the reference's own CUDA tests (its tests/test_cuda.py), read from the reference checkout at
+    generation time: the example files with the substitutions and constants those tests use, and the program texts
+    the tests define inline (found by walking the test module's syntax tree, so no text is restated here).
+    Yields (fixture name, program text, path for diagnostics, constants, standard input)."""
+    import ast
+
+    def example(name, replace=()):
+        path = os.path.join(reference, "examples", f"{name}.anvil")
+        src = open(path).read()
+        for old, new in replace:
+            assert old in src, old
+            src = src.replace(old, new)
+        return src, path
+    for name in ("hello", "linear_regression", "attention"):
+        src, path = example(name)
+        yield f"ref_{name}", src, path, None, ""
+    src, path = example("snake", [("sleep(0.05)", "sleep(0.0)")])
+    yield "ref_snake", src, path, {"EPISODES": 4}, ""
+    src, path = example("checkers", [("sleep(0.15)", "sleep(0.0)"), ("{clock() - start:.1f}s", "{0 * start:.1f}s")])
+    yield "ref_checkers", src, path, {"GAMES": 3, "MATCH": 2, "MAX_PLY": 30, "PLAY": 1, "PLAY_DEPTH": 2,
+                                      "SAVE": "/nonexistent/c.weights"}, "3\n9\nx\n1\n1\n"
+    # The two examples that read files get synthetic stand-ins of the same layout (the text the language model
+    # trains on, the digit images of the diffusion model): tests/programs/data/make_data.py writes them from a seed.
+    sys.path.insert(0, os.path.join(ROOT, "tests", "programs", "data"))
+    import make_data
+    corpus = os.path.join(ROOT, "tests", "programs", "data", "corpus.txt")
+    make_data.write_corpus(corpus)
+    src, path = example("transformer", [("{clock() - start:.1f}s", "{0 * start:.1f}s"), ("step % 250 == 249", "step % 5 == 4"),
+                                        ('bytes("../README.md")', f'bytes("{corpus}")')])
+    yield "ref_transformer", src, path, {"STEPS": 20, "BATCH": 4, "T": 8, "D": 16, "HEADS": 2, "SAMPLE": 10}, ""
+    digits = "/tmp/anvil_synthetic_digits"
+    os.makedirs(digits, exist_ok=True)
+    make_data.write_digit_set(digits)
+    src, path = example("diffusion", [("{clock() - start:.1f}s", "{0 * start:.1f}s"),
+                                      ('idx("data/train-images-idx3-ubyte.gz")', f'idx("{digits}/train-images-idx3-ubyte.gz")'),
+                                      ('idx("data/train-labels-idx1-ubyte.gz")', f'idx("{digits}/train-labels-idx1-ubyte.gz")')])
+    yield "ref_diffusion", src, path, {"EPOCHS": 1, "T": 8, "H": 16, "BATCH": 3000, "PER_DIGIT": 1}, ""
+    tree = ast.parse(open(os.path.join(reference, "tests", "test_cuda.py")).read())
+    texts = {}
+    for node in tree.body:                                   # module-level NAME = """program"""
+        if isinstance(node, ast.Assign) and isinstance(node.value, ast.Constant) and isinstance(node.value.value, str):
+            texts[node.targets[0].id] = node.value.value
+    yield "ref_split", texts["SPLIT"], "<test>.anvil", None, ""
+    for fn in (n for n in tree.body if isinstance(n, ast.FunctionDef)):
+        strings = [c.value for c in ast.walk(fn) if isinstance(c, ast.Constant) and isinstance(c.value, str)
+                   and "\n" in c.value and c.value != ast.get_docstring(fn)]
+        if fn.name == "test_scatter_add_and_gather":
+            yield "ref_scatter_gather", strings[0], "<test>.anvil", None, ""
+        elif fn.name == "test_runtime_bounds_check":
+            yield "ref_bounds_loop", strings[0], "<test>.anvil", None, ""
+        elif fn.name == "test_gather_out_of_bounds_inside_a_kernel":
+            yield "ref_bounds_gather", strings[0], "<test>.anvil", None, ""
+        elif fn.name == "test_save_load_and_assert":
+            yield "ref_assert", [s_ for s_ in strings if "assert x < 2" in s_][0], "<test>.anvil", None, ""
+
+
+def do_reftests(reference, names):
+    """Fixtures `ref_*`: the IR the reference front end makes of those programs, what its interpreter prints, the exit
+    status and error text, and the standard input fed to it."""
+    from anvil.driver import compile_text
+    from anvil_lang_b200 import kir
+    for name, src, path, consts, stdin in reference_test_programs(reference):
+        if names and name not in names:
+            continue
+        t = time.time()
+        c = compile_text(src, path=path, consts=consts)
+        k = kir.from_anvil(c.program, f"{name} (reference tests/test_cuda.py)")
+        kir.dump(k, os.path.join(HERE, f"{name}.kir.json.gz"))
+        text, meta, it = run_reference(c.program, stdin=stdin)
+        meta["stdin"] = stdin
+        with open(os.path.join(HERE, f"{name}.out.txt"), "w") as f:
+            f.write(text)
+        with open(os.path.join(HERE, f"{name}.meta.json"), "w") as f:
+            json.dump(meta, f)
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"))            # text-level fixtures: no tensors kept
+        print(f"{name}: {len(k.kernels())} kernels, exit {meta['exit']} {meta['error'][:60]!r}, "
+              f"{os.path.getsize(os.path.join(HERE, f'{name}.kir.json.gz')) // 1024} KB, {time.time() - t:.1f}s", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["programs", "configs", "functions", "traj", "dp"])
+    ap.add_argument("what", choices=["programs", "configs", "functions", "traj", "dp", "reftests"])
     ap.add_argument("args", nargs="*")
     ap.add_argument("--reference", default=os.environ.get("ANVIL_REFERENCE", os.path.join(os.path.dirname(ROOT), "reference")))
     a = ap.parse_args()
@@ -230,6 +310,8 @@ def main():
         do_functions()
     elif a.what == "dp":
         do_dp()
+    elif a.what == "reftests":
+        do_reftests(a.reference, a.args)
     else:
         name, steps = a.args[0], int(a.args[1])
         consts = json.loads(a.args[2]) if len(a.args) > 2 else None

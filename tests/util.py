@@ -19,9 +19,11 @@ GOLDEN = os.path.join(ROOT, "tests", "golden")
 NUM = re.compile(r"-?\d+\.\d+(?:e[+-]?\d+)?|-?\d+(?:e[+-]?\d+)?|-?inf|nan")
 
 
-def golden_names():
+def golden_names(reference_tests=False):
+    """Fixture programs with a recorded output: the project's own texts, or (reference_tests=True) the programs of the
+    reference's CUDA tests, which run as child processes with their own standard input."""
     names = sorted(os.path.basename(p)[:-len(".kir.json.gz")] for p in glob.glob(os.path.join(GOLDEN, "*.kir.json.gz")))
-    return [n for n in names if os.path.exists(os.path.join(GOLDEN, f"{n}.out.txt"))]
+    return [n for n in names if os.path.exists(os.path.join(GOLDEN, f"{n}.out.txt")) and n.startswith("ref_") == reference_tests]
 
 
 def load_golden(name):
