@@ -359,11 +359,11 @@ def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256, sha
     for r in roots:
         if r.id in offsets:
             continue
-        if share and r.id not in uses and r.kind in SHARED_KINDS and r.init is None and r.id not in keep \
-                and up(max(r.nbytes, 16)) <= plan.shared_bytes:
-            offsets[r.id] = shared_base              # nothing reads or writes it: no bytes of its own
-            plan.unused.add(r.id)
-            continue
+        if r.id not in uses and r.kind in SHARED_KINDS and r.init is None and r.id not in keep:
+            plan.unused.add(r.id)                    # nothing reads or writes it: no bytes of its own
+            if share:
+                offsets[r.id] = scratch_off          # (a valid address; DeviceProgram refuses to copy to or from it)
+                continue
         offsets[r.id] = pos
         pos += up(max(r.nbytes, 16))
     plan.size = pos

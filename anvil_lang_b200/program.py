@@ -76,6 +76,9 @@ class DeviceProgram:
     # ---- tensors
     def read(self, b: kir.Buffer) -> np.ndarray:
         out = np.empty(max(b.numel, 1), dtype=np.int32 if b.dtype == kir.I32 else np.float32)
+        if b.root.id in self.plan.unused:            # a tensor no kernel touches has no memory: it reads as zeros
+            out[:] = 0
+            return out[:b.numel].reshape(b.shape)
         self._check(self.rtlib.anvil_rt_d2h(self.rt, out.ctypes.data, self.plan.off(b), out.nbytes))
         return out[:b.numel].reshape(b.shape)
 
@@ -83,6 +86,8 @@ class DeviceProgram:
         a = np.ascontiguousarray(value, dtype=np.int32 if b.dtype == kir.I32 else np.float32).reshape(-1)
         if a.size != max(b.root.numel, 1) and a.size != b.numel:
             raise ValueError(f"{b.name}: expected {b.numel} elements, got {a.size}")
+        if b.root.id in self.plan.unused:            # no kernel touches it: nothing to write to
+            return
         self._check(self.rtlib.anvil_rt_h2d(self.rt, self.plan.off(b), a.ctypes.data, a.nbytes))
 
     def buffer(self, name: str) -> kir.Buffer:

@@ -75,8 +75,8 @@ def run_case(case, tc):
     if extra == "adam_m":                                  # the moment is linear in the product: same bar
         want_m = 0.9 * m0.astype(np.float64).reshape(batch, M, N) + 0.1 * contraction_acc(a, b, M, N, K, batch, ta, tb, relu_a, alpha)
         err = max(err, np.abs(got_m - want_m).max() / max(np.abs(want_m).max(), 1e-30))
-    else:
-        assert np.array_equal(got_m.reshape(-1), m0.astype(np.float64))      # untouched
+    else:                                                  # no kernel touches Mo here: it has no memory and reads as zeros
+        assert not got_m.any()
     return err, note
 
 

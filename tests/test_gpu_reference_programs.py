@@ -38,7 +38,7 @@ def data_dir(tmp_path_factory):
 def run_child(name, data_dir, stdin):
     env = dict(os.environ, ANVIL_DATA=data_dir, PYTHONPATH=ROOT)
     return subprocess.run([sys.executable, "-m", "anvil_lang_b200.cuda", os.path.join(GOLDEN, f"{name}.kir.json.gz")],
-                          input=stdin, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
+                          input=stdin, capture_output=True, encoding="utf-8", errors="replace", timeout=900, env=env, cwd=ROOT)
 
 
 @pytest.mark.parametrize("name", NAMES)
