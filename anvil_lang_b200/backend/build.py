@@ -119,6 +119,7 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_load_bytes": (I, [P, c.c_char_p, Z, L]), "anvil_rt_input": (I, [P, Z, c.POINTER(I)]),
         "anvil_rt_d2d_async": (I, [P, Z, P, Z, P]),
         "anvil_rt_profile": (None, [P, I]), "anvil_rt_check": (None, [P, I]),
+        "anvil_rt_profile_get": (I, [P, I, c.POINTER(c.c_double), c.POINTER(L)]),
         "anvil_rt_h2d": (I, [P, Z, P, Z]), "anvil_rt_d2h": (I, [P, P, Z, Z]),
         "anvil_rt_h2d_async": (I, [P, Z, P, Z]), "anvil_rt_d2h_async": (I, [P, P, Z, Z]),
         "anvil_rt_zero": (I, [P, Z, Z]), "anvil_rt_sync": (I, [P]),

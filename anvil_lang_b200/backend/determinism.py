@@ -6,8 +6,9 @@ the result — change from run to run. Two IR-to-IR rewrites remove the atomics:
 
   * gathered target (`dE[x[b, t], d] += de[b, t, d]`, the embedding gradient): the kernel is inverted
     into a reduction over the points that carry the index, one output per target element:
-        dE[r, d] += sum_{b, t} (de[b, t, d] if x[b, t] == r else 0)
-    The reduction runs through the ordinary fixed-tree reduction kernels. Used when the indexed
+        dE[r, d] += sum_{b, t} (x[b, t] == r) * de[b, t, d]
+    The reduction runs through the ordinary fixed-order kernels: a contraction template when it is large enough (it is
+    a product of a one-hot matrix with the values), the fixed-tree reduction kernels otherwise. Used when the indexed
     dimension has at most MAX_ROWS entries (the cost is rows x sources comparisons).
     An index outside [0, bound) matches no row and is dropped (the reference reports a fault there).
 
@@ -99,11 +100,14 @@ def invert_gather(k: kir.Kernel, ids) -> Kernel | None:
     if set(plain) - set(other):
         return None
     r = Var(next(ids), "row", g.hi)
+    # one-hot(index == row) * value: a product, so that a large scatter (an embedding gradient) is recognised as the
+    # contraction  one_hot[rows, points] @ values[points, d]  and runs on the tensor-core template (1.0 and 0.0 are exact
+    # there). A select would be the same sum for finite values; a non-finite value now reaches every row of its column.
     hit = E("bin", F32, op="eq", a=[E("load", I32, buf=g.buf, off=g.offset), E("index", I32, off=Affine(0, [(r, 1)]))])
-    body = E("sel", F32, a=[hit, st.value, E("const", F32, val=0.0)])
+    body = E("bin", F32, op="mul", a=[hit, st.value])
     target = Affine(st.offset.const, [(r, cg)] + st.offset.var_terms())
     return Kernel(next(ids), k.name + "_inv", k.label, [r] + other,
-                  [Store(st.buf, target, E("acc", F32), True)], Reduction([v for v in k.domain if v in src_vars], "sum", body))
+                  [Store(st.buf, target, E("acc", F32), True)], Reduction([v for v in k.domain if v in src_vars], "sum", body), src=k.src)
 
 
 def phase_split(k: kir.Kernel, ids) -> list | None:
@@ -126,7 +130,7 @@ def phase_split(k: kir.Kernel, ids) -> list | None:
     out = []
     for values in itertools.product(*[range(v.extent) for v in phase]):
         m = dict(zip(phase, values))
-        out.append(Kernel(next(ids), f"{k.name}_p{'_'.join(map(str, values))}", k.label, rest, _copy_stmts(k, m, ids), None))
+        out.append(Kernel(next(ids), f"{k.name}_p{'_'.join(map(str, values))}", k.label, rest, _copy_stmts(k, m, ids), None, src=k.src))
     return out
 
 

@@ -151,7 +151,7 @@ def merge(P: Kernel, C: Kernel, ids, droppable: set) -> Kernel | None:
     if not mg.ok:
         return None
     fused = Kernel(next(ids), f"{P.name}+{C.name}", f"{P.label}+{C.label}" if C.label else P.label, list(P.domain), stmts,
-                   P.red, P.rand_base)
+                   P.red, P.rand_base, P.src)
     # two stores to one tensor (P's and C's) would make the second one the only live one: drop the first
     last = {}
     for i, st in enumerate(fused.stmts):

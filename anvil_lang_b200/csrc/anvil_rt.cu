@@ -719,6 +719,13 @@ extern "C" int anvil_rt_profile_report(anvil_rt *rt, const char *const *names, i
     emit(rt, line, 0);
     return 0;
 }
+extern "C" int anvil_rt_profile_get(anvil_rt *rt, int slot, double *milliseconds, long *calls) {
+    auto it = rt->prof.find(slot);
+    if (it == rt->prof.end()) { *milliseconds = 0; *calls = 0; return 1; }
+    *milliseconds = it->second.first;
+    *calls = it->second.second;
+    return 0;
+}
 extern "C" long anvil_rt_launch_count(anvil_rt *rt) { return rt->launches; }
 extern "C" void anvil_rt_count_launches(anvil_rt *rt, long n) { rt->launches += n; }
 

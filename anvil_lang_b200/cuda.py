@@ -74,6 +74,11 @@ def main(argv=None) -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--profile", action="store_true", help="time every kernel and print a breakdown at exit")
     ap.add_argument("--check", nargs="?", const="nan", choices=["nan", "inf"], help="stop at the first nan (or infinity) a kernel writes")
+    ap.add_argument("--cost", action="store_true", help="`anvil cost --cuda`: the static FLOP / traffic estimate per source "
+                    "line beside the time measured on the device and its share of the roofline")
+    ap.add_argument("--gpus", type=int, default=int(__import__("os").environ.get("ANVIL_GPUS", "1")),
+                    help="data-parallel run over this many GPUs of the node (also ANVIL_GPUS); needs the program compiled "
+                    "for the per-rank batch, see anvil_lang_b200.dp")
     args = ap.parse_args(argv)
     if args.file.endswith((".json", ".json.gz")):
         prog = kir.load(args.file)
@@ -83,7 +88,56 @@ def main(argv=None) -> int:
     if args.emit:
         print(generate(prog, args.seed))
         return 0
+    if args.cost:
+        from . import cost as _cost
+        c = _cost.program_cost(prog)                     # before the emitter rewrites the program: the source's own kernels
+        ms = _cost.measure(prog, c, seed=args.seed)
+        print(_cost.report(prog, args.file, measured_ms=ms, cost=c))
+        return 0
+    if args.gpus > 1:
+        return run_data_parallel(prog, args, argv)
     return run(prog, seed=args.seed, graphs=not args.no_graphs, profile=args.profile, check=args.check)
+
+
+def run_data_parallel(prog, args, argv) -> int:
+    """`--gpus N` / ANVIL_GPUS: one process per GPU. The first call starts N copies of this command with the
+    rendezvous in the environment (RANK, WORLD_SIZE, LOCAL_RANK, MASTER_ADDR = 127.0.0.1, a free MASTER_PORT) and
+    returns rank 0's exit status; each copy shards the program (`dp.shard`: the program must have been compiled for
+    the per-rank batch), joins the NCCL process group and runs. Only rank 0 prints."""
+    import os
+    import subprocess
+    if "RANK" not in os.environ:
+        import socket
+        sock = socket.socket()
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+        sock.close()
+        cmd = [sys.executable, "-m", "anvil_lang_b200.cuda"] + list(argv if argv is not None else sys.argv[1:])
+        procs = [subprocess.Popen(cmd, env=dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(args.gpus),
+                                                 MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ANVIL_GPUS=str(args.gpus)))
+                 for r in range(args.gpus)]
+        codes = [p.wait() for p in procs]
+        return codes[0] if codes[0] != 0 else max(codes)
+    import torch
+    import torch.distributed as dist
+    from . import dp as _dp
+    rank, world, dev = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{dev}"))
+    try:
+        sharded = _dp.shard(as_kir(prog), world)
+        devprog = DeviceProgram(sharded, seed=args.seed, device=dev, graphs=not args.no_graphs)
+        try:
+            devprog.set_rank(rank)
+            _dp.attach(devprog, dev)
+            code, _ = devprog.run(capture=rank != 0)
+            if code == 1 and devprog.error and rank == 0:
+                print(devprog.error, file=sys.stderr)
+            return code
+        finally:
+            devprog.close()
+    finally:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -138,7 +138,7 @@ def shard(prog: kir.Program, world: int) -> kir.Program:
         prog.buffers.append(g)
         grads.append(g)
         ident = _identity(k.domain)
-        first.append(Kernel(next(ids), k.name + "_g", k.label, k.domain, [Store(g, ident, E("acc", F32))], k.red))
+        first.append(Kernel(next(ids), k.name + "_g", k.label, k.domain, [Store(g, ident, E("acc", F32))], k.red, src=k.src))
         lets, memo, stmts = {}, {}, []
 
         def fn(n, g=g, ident=ident):
@@ -152,7 +152,7 @@ def shard(prog: kir.Program, world: int) -> kir.Program:
                 stmts.append(nl)
             else:
                 stmts.append(Store(st.buf, st.offset, _rewrite(st.value, fn, memo, lets), st.accumulate))
-        updates.append(Kernel(next(ids), k.name + "_u", k.label, k.domain, stmts, None))
+        updates.append(Kernel(next(ids), k.name + "_u", k.label, k.domain, stmts, None, src=k.src))
 
     # gradients that reach an update kernel through memory (written by non-update kernels)
     written_first = set()
@@ -183,7 +183,7 @@ def shard(prog: kir.Program, world: int) -> kir.Program:
                 stmts.append(nl)
             else:
                 stmts.append(Store(st.buf, st.offset, _rewrite(st.value, fn2, memo, lets), st.accumulate))
-        updates[i] = Kernel(k.id, k.name, k.label, k.domain, stmts, None, k.rand_base)
+        updates[i] = Kernel(k.id, k.name, k.label, k.domain, stmts, None, k.rand_base, k.src)
 
     # moving the updates to the end must not change what anything reads
     upd_writes = set()

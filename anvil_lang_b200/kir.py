@@ -271,6 +271,8 @@ class Kernel:
     red: Reduction | None = None
     rand_base: object = None   # (i32 0-d Buffer, coef): coef * buffer value is added to the element index of
                                # every random draw (a rank's slice of a global tensor)
+    src: object = None         # (file path, line number, text of the line) of the source statement, when known
+                               # (reference anvil/ir.py: `Kernel.span`); cost reports and --check messages use it
 
     @property
     def stores(self):
@@ -615,7 +617,15 @@ class _Importer:
             else:
                 stmts.append(Store(self.buffer(s.buf), self.affine(s.offset), self.expr(s.value, memo),
                                    bool(s.accumulate)))
-        return Kernel(int(k.id), str(k.name or f"k{k.id}"), str(k.label or ""), domain, stmts, red)
+        src = None
+        span = getattr(k, "span", None)
+        if span is not None and getattr(span, "file", None) is not None:
+            try:
+                text = span.file.line_text(span.line).strip()
+            except Exception:
+                text = ""
+            src = (str(span.file.path).replace("\\", "/").rsplit("/", 1)[-1], int(span.line), text[:200])   # the file's name, not where it lay
+        return Kernel(int(k.id), str(k.name or f"k{k.id}"), str(k.label or ""), domain, stmts, red, None, src)
 
     def bound(self, x):
         return int(x) if isinstance(x, int) else self.buffer(x)
@@ -731,6 +741,8 @@ class _Writer:
                 stmts.append(["store", s.buf.id, self.aff(s.offset), put(s.value), 1 if s.accumulate else 0])
         out["stmts"] = stmts
         out["nodes"] = nodes
+        if k.src is not None:
+            out["src"] = list(k.src)
         return out
 
     def bound(self, x):
@@ -857,7 +869,8 @@ class _Reader:
                 stmts.append(let)
             else:
                 stmts.append(Store(self.bufs[s[1]], self.aff(s[2]), built[s[3]], bool(s[4])))
-        return Kernel(d["id"], d["name"], d["label"], domain, stmts, red)
+        src = tuple(d["src"]) if d.get("src") else None
+        return Kernel(d["id"], d["name"], d["label"], domain, stmts, red, None, src)
 
     def bound(self, x):
         return x if isinstance(x, int) else self.bufs[x["buf"]]

@@ -156,6 +156,9 @@ void anvil_rt_profile(anvil_rt *rt, int on);
 int anvil_rt_prof_begin(anvil_rt *rt, int slot);
 int anvil_rt_prof_end(anvil_rt *rt, int slot);
 int anvil_rt_profile_report(anvil_rt *rt, const char *const *names, int n);
+/* What --profile has accumulated for one launch unit so far: total milliseconds and calls; 1 if it never ran.
+ * (`anvil cost --cuda` puts these beside the static estimate of anvil/cost.py:116-150.) */
+int anvil_rt_profile_get(anvil_rt *rt, int slot, double *milliseconds, long *calls);
 long anvil_rt_launch_count(anvil_rt *rt);          /* kernels launched (graph replays count their nodes) */
 void anvil_rt_count_launches(anvil_rt *rt, long n);
 
