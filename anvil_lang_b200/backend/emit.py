@@ -892,7 +892,7 @@ class KernelGen:
             S = max(1, min(296 // (tiles * NB), K // 128, 32))
         AK, BNC = ("true" if c.a_kcontig else "false"), ("true" if c.b_ncontig else "false")
         fn = f"G{k.id}"
-        if use_tensor_cores() and K % 4 == 0 and c.kvars[-1].extent % 4 == 0 and M >= 96 and N >= 64 and K >= 64 \
+        if use_tensor_cores() and K % 4 == 0 and M >= 96 and N >= 64 and K >= 64 \
                 and c.flops >= tc_min_flops():
             return self.gen_gemm_tc(base, c, fn, fa, fb, fe, S)
         src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (CUDA-core tiles, split {S})"),
@@ -926,6 +926,22 @@ class KernelGen:
         self.ptrs = {}
         vv = kvars[-1]
         ind = "        "
+        if vv.extent % 4:
+            # the innermost reduction index is not a multiple of 4 long (a 3 x 3 window): the four k are decoded one by one
+            lines, vals = [], []
+            for lane in range(4):
+                names = dict(self.names)
+                for v in kvars:
+                    names[v] = f"{self.names[v]}_{lane}"
+                lines += self.decode(f"(uint32_t)(k + {lane})", kvars, names, ind)
+                sc = Scope(self, names, 1, None, ind)
+                vals.append(sc.ex(operand, 0))
+                lines += sc.lines
+            decls = ["    " + ln for ln in self.pointer_decls()]
+            out = [f"    __device__ __forceinline__ {sig} const {{"] + decls + pre + lines
+            out += [f"{ind}v[{i}] = {x};" for i, x in enumerate(vals)] + ["    }"]
+            self.ptrs = {**saved, **self.ptrs}
+            return out
         dk = self.decode("((uint32_t)k >> 2)", kvars, self.names, ind, vv, 4) + self.lane_vars(vv, 4, ind)
         sc = Scope(self, self.names, 4, vv, ind)
         vals = [sc.ex(operand, lane) for lane in range(4)]
@@ -1749,6 +1765,10 @@ class ProgramGen:
 def generate(prog: kir.Program, seed: int = 0):
     """Returns (source text, ProgramGen). Generated twice when split reductions need scratch space,
     because the scratch region sits in front of the buffers."""
+    if os_environ("ANVIL_B200_IMPLICIT", "1") != "0":
+        from .implicit import make_implicit
+        from .refuse import _host_reads
+        make_implicit(prog, _host_reads(prog))       # window copies (im2col) and their scattered gradients fold into the products
     if os_environ("ANVIL_B200_DETERMINISTIC", "1") != "0":
         from .determinism import make_deterministic
         make_deterministic(prog)                     # colliding `+=` get a fixed order (idempotent)

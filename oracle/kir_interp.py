@@ -597,7 +597,13 @@ class Oracle:
         if k == "const":
             return np.asarray(e.val, dtype=np.int32 if e.dt == I32 else fdt)
         if k == "load":
-            return self.arr(e.buf)[self.affine(e.off, ctx["env"], ctx)]
+            idx = self.affine(e.off, ctx["env"], ctx)
+            if any(c < 0 for t, c in e.off.terms if isinstance(t, kir.Var)):
+                # A load under a range guard (`x[y - u] if 0 <= y - u < n else 0`, which the back end's implicit
+                # convolution rewrite makes): NumPy evaluates both branches, so the index is clamped; the guard
+                # discards the value. The reference's own IR never has a negative stride.
+                idx = np.clip(idx, 0, self.arr(e.buf).size - 1)
+            return self.arr(e.buf)[idx]
         if k == "index":
             return np.asarray(self.affine(e.off, ctx["env"], ctx), dtype=np.int32)
         if k == "acc":
