@@ -161,10 +161,9 @@ def _copy_kernel(k: Kernel):
     dims = _dims_of_identity(k, st)
     if dims is None:
         return None
-    loads = [n for n in st.value.walk() if n.k == "load"]
-    if not loads or any(not n.off.is_plain() for n in loads) or any(n.k in ("rand", "acc") for n in st.value.walk()):
-        return None
-    if all(an.injective_over(n.off, k.domain) for n in loads):
+    if st.value.k != "load" or not st.value.off.is_plain():
+        return None                                      # only pure copies: anything computed is worth computing once
+    if an.injective_over(st.value.off, k.domain):
         return None                                      # a plain permutation: the optimizer's business, nothing to gain
     return st.buf.root, dims, st.value
 
