@@ -32,6 +32,7 @@ from .. import kir
 from ..kir import F32, I32
 from . import analysis as an
 from . import contraction as ct
+from . import hfuse
 from . import rowgroup as rg
 
 THREADS = 256
@@ -813,6 +814,22 @@ class KernelGen:
     def gen_gemm(self, base, c):
         k = self.k
         M, N, K, NB = c.M, c.N, c.K, c.NB
+        fa, fb, fe = self.gemm_functors(c)
+        tiles = ((M + 127) // 128) * ((N + 127) // 128)
+        S = 1
+        if tiles * NB < 148 and K >= 256:
+            S = max(1, min(296 // (tiles * NB), K // 128, 32))
+        AK, BNC = ("true" if c.a_kcontig else "false"), ("true" if c.b_ncontig else "false")
+        fn = f"G{k.id}"
+        if tc_eligible(c):
+            return self.gen_gemm_tc(base, c, fn, fa, fb, fe, S)
+        return self.gen_gemm_simt(base, c, fn, fa, fb, fe, S, tiles, AK, BNC)
+
+    def gemm_functors(self, c):
+        """The functor methods every contraction template takes: a / b (one operand element), epi (the statements on
+        one accumulator), epi_touch (L2 prefetch of what they read), and the two-phase form epi_loads / epi2."""
+        k = self.k
+        M, N, K, NB = c.M, c.N, c.K, c.NB
         ind = "        "
         dm = self.decode("(uint32_t)m", c.mvars, self.names, ind)
         dn = self.decode("(uint32_t)n", c.nvars, self.names, ind)
@@ -886,15 +903,12 @@ class KernelGen:
         fe = fe + [f"    static constexpr int NLD = {nld};"]
         fe = fe + self.functor_method(f"void epi_loads(int m, int n, int bt, float (&ld)[{max(nld, 1)}])", dm + dn + db, loads)
         fe = fe + self.functor_method(f"void epi2(int m, int n, int bt, float acc, const float (&ld)[{max(nld, 1)}])", dm + dn + db, epi2)
-        tiles = ((M + 127) // 128) * ((N + 127) // 128)
-        S = 1
-        if tiles * NB < 148 and K >= 256:
-            S = max(1, min(296 // (tiles * NB), K // 128, 32))
-        AK, BNC = ("true" if c.a_kcontig else "false"), ("true" if c.b_ncontig else "false")
-        fn = f"G{k.id}"
-        if use_tensor_cores() and K % 4 == 0 and M >= 96 and N >= 64 and K >= 64 \
-                and c.flops >= tc_min_flops():
-            return self.gen_gemm_tc(base, c, fn, fa, fb, fe, S)
+        self.nld = nld
+        return fa, fb, fe
+
+    def gen_gemm_simt(self, base, c, fn, fa, fb, fe, S, tiles, AK, BNC):
+        k = self.k
+        M, N, K, NB = c.M, c.N, c.K, c.NB
         src = [self.comment(f"contraction M={M} N={N} K={K} batch={NB} (CUDA-core tiles, split {S})"),
                f"struct {fn} {{", "    char *__restrict__ A;",
                f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = {NB};",
@@ -951,18 +965,15 @@ class KernelGen:
         self.ptrs = {**saved, **self.ptrs}
         return out
 
-    def gen_gemm_tc(self, base, c, fn, fa, fb, fe, S):
-        k = self.k
-        M, N, K, NB = c.M, c.N, c.K, c.NB
+    def tc_operands(self, c, touch: bool):
+        """a4 / b4 (four consecutive k of one operand row) and, for the resident template, a_touch / b_touch."""
         ind = "        "
         dm = self.decode("(uint32_t)m", c.mvars, self.names, ind)
         dn = self.decode("(uint32_t)n", c.nvars, self.names, ind)
         db = self.decode("(uint32_t)bt", c.bvars, self.names, ind) if c.bvars else []
         fa4 = self.functor4("void a4(int m, int k, int bt, float (&v)[4])", c, c.a, dm + db, c.kvars)
         fb4 = self.functor4("void b4(int k, int n, int bt, float (&v)[4])", c, c.b, dn + db, c.kvars)
-        nstores = sum(1 for st in k.stmts if isinstance(st, kir.Store))
-        variant = tc_variant(c.a_kcontig, M, N, K, nstores)
-        if variant == "pp":                      # L2 prefetch of the operand element (m, k) / (k, n): issued some blocks ahead
+        if touch:                                # L2 prefetch of the operand element (m, k) / (k, n): issued some blocks ahead
             dks = self.decode("(uint32_t)k", c.kvars, self.names, ind)
 
             def operand_touch(operand):
@@ -976,6 +987,20 @@ class KernelGen:
                 return build
             fa4 = fa4 + self.functor_method("void a_touch(int m, int k, int bt)", dm + dks + db, operand_touch(c.a))
             fb4 = fb4 + self.functor_method("void b_touch(int k, int n, int bt)", dn + dks + db, operand_touch(c.b))
+        return fa4, fb4
+
+    def tc_struct(self, c, fn, fe, touch: bool) -> list[str]:
+        fa4, fb4 = self.tc_operands(c, touch)
+        return [f"struct {fn} {{", "    char *__restrict__ A;",
+                f"    static constexpr int M = {c.M}, N = {c.N}, K = {c.K}, NB = {c.NB};",
+                f"    static constexpr float ALPHA = {flit(c.alpha)};"] + fa4 + fb4 + fe + ["};"]
+
+    def gen_gemm_tc(self, base, c, fn, fa, fb, fe, S):
+        k = self.k
+        M, N, K, NB = c.M, c.N, c.K, c.NB
+        nstores = sum(1 for st in k.stmts if isinstance(st, kir.Store))
+        variant = tc_variant(c.a_kcontig, M, N, K, nstores)
+        fa4, fb4 = self.tc_operands(c, variant == "pp")
         pp = variant == "pp"
         pair = variant == "pair" or pp
         if pair:                                 # 256 x BN tile per cluster of two CTAs
@@ -1055,6 +1080,26 @@ def os_environ(name: str, default: str) -> str:
     return os.environ.get(name, default)
 
 
+def use_hgroups() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_HGROUPS", "1") != "0" and os.environ.get("ANVIL_B200_TC", "1") in ("1", "pp")
+
+
+def tc_eligible_pp(c) -> bool:
+    """Takes the resident pair template by the emitter's own choice."""
+    nstores = sum(1 for st in c.kernel.stmts if isinstance(st, kir.Store))
+    return tc_eligible(c) and tc_variant(c.a_kcontig, c.M, c.N, c.K, nstores) == "pp"
+
+
+def fused_runs(kernels):
+    """Index ranges of consecutive kernels that run as ONE launch (fused row groups, horizontal contraction groups):
+    the arena planner treats each as one statement."""
+    out = list(rg.find_groups(kernels)) if use_row_groups() else []
+    if use_hgroups():
+        out += [(a, b) for a, b, _ in hfuse.find_hgroups(kernels, tc_eligible_pp)]
+    return out
+
+
 def use_row_groups() -> bool:
     import os
     return os.environ.get("ANVIL_B200_ROWGROUPS", "1") != "0"
@@ -1063,6 +1108,26 @@ def use_row_groups() -> bool:
 def use_tensor_cores() -> bool:
     import os
     return os.environ.get("ANVIL_B200_TC", "1") != "0"
+
+
+def tc_eligible(c) -> bool:
+    """Does this contraction take a tensor-core template? K must be a multiple of 4 (operands are converted four
+    consecutive k at a time), the tile must not be mostly empty, and the product must be worth a tensor-core launch."""
+    return use_tensor_cores() and c.K % 4 == 0 and c.M >= 96 and c.N >= 64 and c.K >= 64 and c.flops >= tc_min_flops()
+
+
+def pp_launch_params(M, N, K, NB):
+    """(BN, split, accumulators, work items) of the resident pair template for a shape."""
+    BN = 256 if N >= 256 else 128 if N >= 128 else 64
+    if BN == 256 and K <= 1024 and ((M + 255) // 256) * ((N + 255) // 256) * NB < 74:
+        BN = 128                         # too few 256-wide tiles for the 74 clusters: narrower tiles before any k split
+    tiles = ((M + 255) // 256) * ((N + BN - 1) // BN)
+    S = 1
+    if tiles * NB < 74 and K >= 256:
+        S = max(1, min(74 // (tiles * NB), K // 128, 32))
+    S = max(S, (K + 4095) // 4096)       # one accumulation chain stays <= 4096 long (rounding, see the template's header)
+    accs = 1 if (K + S - 1) // S <= 512 and BN == 256 else 2
+    return BN, S, accs, tiles * NB * S
 
 
 def tc_min_flops() -> int:
@@ -1254,6 +1319,94 @@ class RowGroupGen:
         return src, launch
 
 
+class HGroupGen:
+    """A horizontal group of contractions (see hfuse.py) -> one launch of the resident pair template over a functor
+    that dispatches to the members' functors by tile column ("ncat") or by reduction block ("kcat")."""
+
+    def __init__(self, gen: "ProgramGen", kernels, kind: str):
+        self.gen, self.kernels, self.kind = gen, kernels, kind
+
+    def generate(self, name: str):
+        gen, ks, kind = self.gen, self.kernels, self.kind
+        cs = [ct.match(k) for k in ks]
+        src, names, nlds = [], [], []
+        for i, (k, c) in enumerate(zip(ks, cs)):
+            kg = KernelGen(gen, k)
+            _, _, fe = kg.gemm_functors(c)
+            fn = f"{name}_{i}"
+            src += [kg.comment(f"member {i} of a fused launch")] + kg.tc_struct(c, fn, fe, True) + [""]
+            names.append(fn)
+            nlds.append(kg.nld)
+        c0 = cs[0]
+        M = c0.M
+        N = sum(c.N for c in cs) if kind == "ncat" else c0.N
+        K = sum(c.K for c in cs) if kind == "kcat" else c0.K
+        nld = max(nlds) if kind == "ncat" else nlds[0]
+        L = max(nld, 1)
+
+        def dispatch(sig, call, sizes, var):
+            """`if (var < s0) member0.call else if ...` with `var` rebased for each member."""
+            out = [f"    __device__ __forceinline__ {sig} const {{"]
+            base = 0
+            for i, (fn, size) in enumerate(zip(names, sizes)):
+                head = "if" if i == 0 else "else if"
+                cond = f"{head} ({var} < {base + size})" if i < len(names) - 1 else ("else" if i else "")
+                shifted = f"{var} - {base}" if base else var
+                out.append(f"        {cond} {{ {fn}{{A}}.{call.format(v=shifted, L=max(nlds[i], 1))}; }}")
+                base += size
+            return out + ["    }"]
+        kernel_name, name = name, "F_" + name               # the functor type; the __global__ function keeps the plain name
+        f = [f"// {kind}: " + " | ".join(f"{k.name} <{k.label}>" for k in ks), f"struct {name} {{", "    char *__restrict__ A;",
+             f"    static constexpr int M = {M}, N = {N}, K = {K}, NB = 1, NLD = {nld};",
+             f"    static constexpr float ALPHA = {flit(c0.alpha)};"]
+        first = names[0]
+        if kind == "ncat":
+            sizes = [c.N for c in cs]
+            f += [f"    __device__ __forceinline__ void a4(int m, int k, int bt, float (&v)[4]) const {{ {first}{{A}}.a4(m, k, bt, v); }}",
+                  f"    __device__ __forceinline__ void a_touch(int m, int k, int bt) const {{ {first}{{A}}.a_touch(m, k, bt); }}"]
+            f += dispatch("void b4(int k, int n, int bt, float (&v)[4])", "b4(k, {v}, bt, v)", sizes, "n")
+            f += dispatch("void b_touch(int k, int n, int bt)", "b_touch(k, {v}, bt)", sizes, "n")
+            f += dispatch("void epi(int m, int n, int bt, float acc)", "epi(m, {v}, bt, acc)", sizes, "n")
+            f += dispatch("void epi_touch(int m, int n, int bt)", "epi_touch(m, {v}, bt)", sizes, "n")
+            f += dispatch(f"void epi_loads(int m, int n, int bt, float (&ld)[{L}])",
+                          "epi_loads(m, {v}, bt, reinterpret_cast<float (&)[{L}]>(ld))", sizes, "n")
+            f += dispatch(f"void epi2(int m, int n, int bt, float acc, const float (&ld)[{L}])",
+                          "epi2(m, {v}, bt, acc, reinterpret_cast<const float (&)[{L}]>(ld))", sizes, "n")
+        else:
+            sizes = [c.K for c in cs]
+            f += dispatch("void a4(int m, int k, int bt, float (&v)[4])", "a4(m, {v}, bt, v)", sizes, "k")
+            f += dispatch("void b4(int k, int n, int bt, float (&v)[4])", "b4({v}, n, bt, v)", sizes, "k")
+            f += dispatch("void a_touch(int m, int k, int bt)", "a_touch(m, {v}, bt)", sizes, "k")
+            f += dispatch("void b_touch(int k, int n, int bt)", "b_touch({v}, n, bt)", sizes, "k")
+            f += [f"    __device__ __forceinline__ void epi(int m, int n, int bt, float acc) const {{ {first}{{A}}.epi(m, n, bt, acc); }}",
+                  f"    __device__ __forceinline__ void epi_touch(int m, int n, int bt) const {{ {first}{{A}}.epi_touch(m, n, bt); }}",
+                  f"    __device__ __forceinline__ void epi_loads(int m, int n, int bt, float (&ld)[{L}]) const {{ {first}{{A}}.epi_loads(m, n, bt, ld); }}",
+                  f"    __device__ __forceinline__ void epi2(int m, int n, int bt, float acc, const float (&ld)[{L}]) const {{ {first}{{A}}.epi2(m, n, bt, acc, ld); }}"]
+        f.append("};")
+        BN, S, accs, work = pp_launch_params(M, N, K, 1)
+        AK = "true" if c0.a_kcontig else "false"
+        BKC = "true" if ct._contig(c0.b, c0.kvars[-1]) else "false"
+        status = "(uint32_t *)(A + ANVIL_RT_STATUS_OFF)"
+        kname = kernel_name + ("_part" if S > 1 else "")
+        smem = f"anvil::tc::pp_smem_bytes({BN})"
+        scratch = "nullptr"
+        if S > 1:
+            gen.need_scratch(4 * M * N * S)
+            scratch = f"(float *)(A + {gen.plan.scratch_off}UL)"
+        f += [f"__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(anvil::tc::PP_THREADS, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+              f"    anvil::tc::gemm_tc_pair_persistent<{name}, {AK}, {BKC}, {S}, {accs}, {BN}>({name}{{A}}, {scratch}, {status});", "}"]
+        launch = [f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
+                  f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}",
+                  f"{kname}<<<dim3({2 * min(work, 74)}, 1), anvil::tc::PP_THREADS, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);"]
+        if S > 1:
+            f += [f"__global__ void __launch_bounds__(256) {kernel_name}_fin(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                  f"    anvil::gemm_split_finish<{name}, {S}>({name}{{A}}, (const float *)(A + {gen.plan.scratch_off}UL));", "}"]
+            fb_ = max(1, min((M * N + 255) // 256, MAX_BLOCKS))
+            launch.append(f"{kernel_name}_fin<<<{fb_}, 256, 0, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        note = f"gemm tc 1x{M}x{N}x{K} S{S} pp {kind}{len(ks)}"
+        return "\n".join(src + f), launch, note
+
+
 def index_t(n: int) -> str:
     return "uint32_t" if n < (1 << 32) else "unsigned long long"
 
@@ -1302,7 +1455,7 @@ class ProgramGen:
         keep = set(self._host_reads())
         if hot is not None:
             keep |= {b.root.id for b in an.input_producers(self.prog, hot)[1]}
-        runs = (lambda ks: rg.find_groups(ks)) if use_row_groups() else None
+        runs = fused_runs
         return an.plan_arena(self.prog, scratch_bytes, share=os_environ("ANVIL_B200_ARENA", "shared") != "unshared",
                              fused_runs=runs, keep=keep)
 
@@ -1391,6 +1544,25 @@ class ProgramGen:
 
     MAX_FAULT_CODES = 254
 
+    def add_hgroup(self, kernels: list, kind: str) -> int:
+        """Launch-table index of the fused launch for a horizontal group of contractions."""
+        key = ("h",) + tuple(k.id for k in kernels)
+        hit = self.groups.get(key)
+        if hit is not None:
+            return hit
+        idx = len(self.groups)
+        src, launch, note = HGroupGen(self, kernels, kind).generate(f"h{idx}_{kernels[0].id}")
+        self.groups[key] = idx
+        self.group_src.append(src)
+        self.group_notes.append(note)
+        body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
+                "    uint32_t seed = anvil_rt_get_seed(rt);", "    uint32_t sdelta = 0;",
+                f"    RT(anvil_rt_prof_begin(rt, PROF_GROUP0 + {idx}));"] + ["    " + ln for ln in launch] \
+            + [f"    RT(anvil_rt_prof_end(rt, PROF_GROUP0 + {idx}));"] + self.check_lines(kernels) + ["    return 0;"]
+        self.group_launchers.append(f"static int launch_group_{idx}(anvil_rt *rt) {{   // {' | '.join(k.name for k in kernels)}\n"
+                                    + "\n".join(body) + "\n}")
+        return idx
+
     def fault(self, message: str) -> int:
         """The code (1-based index into the program's message table) a kernel records for this bounds fault. The
         fault word holds one byte of code: once the table is full, further messages share a generic entry."""
@@ -1477,9 +1649,18 @@ class ProgramGen:
                     j += 1
                 spans = rg.find_groups(run_kernels) if use_row_groups() else []
                 starts = {a: b for a, b in spans}
+                hstarts = {a: (b, kind) for a, b, kind in (hfuse.find_hgroups(run_kernels, tc_eligible_pp) if use_hgroups() else [])}
                 q = 0
                 while q < len(run_kernels):
-                    if q in starts:
+                    if q in hstarts:
+                        end, kind = hstarts[q]
+                        ks = run_kernels[q:end]
+                        gi = self.add_hgroup(ks, kind)
+                        calls.append(f"RT(launch_group_{gi}(rt));")
+                        if self.record_units:
+                            self.hot_units.append((("g", gi), self.group_notes[gi], ks))
+                        q = end
+                    elif q in starts:
                         ks = run_kernels[q:starts[q]]
                         gi = self.add_group(ks)
                         calls.append(f"RT(launch_group_{gi}(rt));")

@@ -112,3 +112,28 @@ def test_continue_in_a_for_loop_still_advances_the_counter():
     for m, body in with_continue:
         assert "anvil_b200_advance(rt," in m.group(0), m.group(0)       # the advance is the loop's third clause
         assert "anvil_rt_add_i32" not in body.split("continue;")[-1]      # not at the bottom of the body
+
+
+def test_transformer_products_are_fused_side_by_side():
+    """Per transformer block: the three products with the same left operand (h @ Wq, h @ Wk, h @ Wv) become one launch
+    with the outputs side by side, so do their three weight gradients, and the three products that add up to the
+    gradient of h become one launch over the concatenated reduction index (backend/hfuse.py)."""
+    import os as _os
+    from collections import Counter
+    from anvil_lang_b200 import kir
+    from util import ROOT
+    prog = kir.load(_os.path.join(ROOT, "anvil_lang_b200", "programs", "c5_transformer.kir.json.gz"))
+    src, g = emit.generate(prog, 0)
+    notes = Counter(n for n in g.group_notes if n.startswith("gemm"))
+    assert notes == {"gemm tc 1x16384x1536x512 S1 pp ncat3": 6, "gemm tc 1x16384x512x1536 S1 pp kcat3": 6,
+                     "gemm tc 1x512x1536x16384 S6 pp ncat3": 6}
+    units = [note for _, note, _ in g.hot_units]
+    assert sum(1 for n in units if n.startswith("gemm tc 1x16384x512x512")) == 12       # Wo forward and its dX remain single
+    assert "if (n < 512)" in src and "else if (n < 1024)" in src and "if (k < 512)" in src
+    os.environ["ANVIL_B200_HGROUPS"] = "0"
+    try:
+        prog = kir.load(_os.path.join(ROOT, "anvil_lang_b200", "programs", "c5_transformer.kir.json.gz"))
+        _, g0 = emit.generate(prog, 0)
+    finally:
+        os.environ.pop("ANVIL_B200_HGROUPS")
+    assert not [n for n in g0.group_notes if n.startswith("gemm")] and len(g0.hot_units) == len(g.hot_units) + 36
