@@ -184,10 +184,10 @@ def covers(k: kir.Kernel, st: kir.Store) -> bool:
 
 
 class _Use:
-    __slots__ = ("pos", "chain", "write", "full")
+    __slots__ = ("pos", "chain", "write", "full", "after")
 
-    def __init__(self, pos, chain, write, full):
-        self.pos, self.chain, self.write, self.full = pos, chain, write, full
+    def __init__(self, pos, chain, write, full, after=False):
+        self.pos, self.chain, self.write, self.full, self.after = pos, chain, write, full, after
 
 
 def _flatten(prog: kir.Program, fused_runs):
@@ -199,16 +199,19 @@ def _flatten(prog: kir.Program, fused_runs):
     loops: list = []
     pos = 0
 
-    def note(b, chain, write=False, full=False):
+    def note(b, chain, write=False, full=False, after=False):
         if isinstance(b, kir.Buffer):
-            uses.setdefault(b.root.id, []).append(_Use(pos, chain, write, full))
+            uses.setdefault(b.root.id, []).append(_Use(pos, chain, write, full, after))
 
-    def kernel_uses(k, chain):
+    def kernel_uses(k, chain, written_in_run):
+        """`written_in_run`: tensors an earlier kernel of the same fused launch has written in full — a read of one of
+        those is not a read of the tensor's initial contents, although it shares the statement position."""
         full = {st.buf.root.id for st in k.stores if covers(k, st)}
         for r in k.reads():
-            note(r, chain)
+            note(r, chain, after=r.id in written_in_run)
         for r in k.writes():
             note(r, chain, True, r.id in full)
+        written_in_run |= full
 
     def block(b: kir.Block, chain):
         nonlocal pos
@@ -226,8 +229,9 @@ def _flatten(prog: kir.Program, fused_runs):
                 while q < len(run):
                     pos += 1
                     end = starts.get(q, q + 1)
+                    seen_full: set = set()
                     for k in run[q:end]:
-                        kernel_uses(k, chain)
+                        kernel_uses(k, chain, seen_full)
                     q = end
                 i = j
                 continue
@@ -286,7 +290,7 @@ def _lifetime(us, loops):
     be certain to have run before every other use (anvil/backend/arena.py:101-118)."""
     first = us[0].pos
     at_first = [u for u in us if u.pos == first]
-    if any(not u.write for u in at_first) or not any(u.full for u in at_first):
+    if any(not u.write and not u.after for u in at_first) or not any(u.full for u in at_first):
         return None
     chain = at_first[0].chain
     if any(u.chain[:len(chain)] != chain for u in us):

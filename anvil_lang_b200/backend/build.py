@@ -83,7 +83,7 @@ def build_program(source: str, path: str | None = None) -> str:
     os.makedirs(BUILD_DIR, exist_ok=True)
     deps = _stamp([os.path.join(CSRC, "anvil_device.cuh"), os.path.join(CSRC, "anvil_rng.h"),
                    os.path.join(CSRC, "anvil_gemm_simt.cuh"), os.path.join(CSRC, "anvil_gemm_sm100.cuh"),
-                   os.path.join(INCLUDE, "anvil_cuda.h")])
+                   os.path.join(CSRC, "anvil_attn_sm100.cuh"), os.path.join(INCLUDE, "anvil_cuda.h")])
     key = hashlib.sha256((source + deps).encode()).hexdigest()[:16]
     lib = path or os.path.join(BUILD_DIR, f"prog-{key}.so")
     if os.path.exists(lib) and path is None:

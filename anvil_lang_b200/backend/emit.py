@@ -31,6 +31,7 @@ import math
 from .. import kir
 from ..kir import F32, I32
 from . import analysis as an
+from . import attention as at
 from . import contraction as ct
 from . import hfuse
 from . import rowgroup as rg
@@ -1080,6 +1081,11 @@ def os_environ(name: str, default: str) -> str:
     return os.environ.get(name, default)
 
 
+def use_attention() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_ATTENTION", "1") != "0" and os.environ.get("ANVIL_B200_TC", "1") in ("1", "pp")
+
+
 def use_hgroups() -> bool:
     import os
     return os.environ.get("ANVIL_B200_HGROUPS", "1") != "0" and os.environ.get("ANVIL_B200_TC", "1") in ("1", "pp")
@@ -1091,12 +1097,16 @@ def tc_eligible_pp(c) -> bool:
     return tc_eligible(c) and tc_variant(c.a_kcontig, c.M, c.N, c.K, nstores) == "pp"
 
 
-def fused_runs(kernels):
-    """Index ranges of consecutive kernels that run as ONE launch (fused row groups, horizontal contraction groups):
-    the arena planner treats each as one statement."""
-    out = list(rg.find_groups(kernels)) if use_row_groups() else []
+def fused_runs(kernels, attention_spans=()):
+    """Index ranges of consecutive kernels that run as ONE launch (fused attention, horizontal contraction groups,
+    fused row groups): the arena planner treats each as one statement."""
+    out = [(a, b) for a, b, _ in attention_spans]
+    more = list(rg.find_groups(kernels)) if use_row_groups() else []
     if use_hgroups():
-        out += [(a, b) for a, b, _ in hfuse.find_hgroups(kernels, tc_eligible_pp)]
+        more += [(a, b) for a, b, _ in hfuse.find_hgroups(kernels, tc_eligible_pp)]
+    for a, b in more:
+        if not any(a < y and x < b for x, y in out):
+            out.append((a, b))
     return out
 
 
@@ -1116,9 +1126,9 @@ def tc_eligible(c) -> bool:
     return use_tensor_cores() and c.K % 4 == 0 and c.M >= 96 and c.N >= 64 and c.K >= 64 and c.flops >= tc_min_flops()
 
 
-def pp_launch_params(M, N, K, NB):
+def pp_launch_params(M, N, K, NB, max_bn=256):
     """(BN, split, accumulators, work items) of the resident pair template for a shape."""
-    BN = 256 if N >= 256 else 128 if N >= 128 else 64
+    BN = 256 if N >= 256 and max_bn >= 256 else 128 if N >= 128 else 64
     if BN == 256 and K <= 1024 and ((M + 255) // 256) * ((N + 255) // 256) * NB < 74:
         BN = 128                         # too few 256-wide tiles for the 74 clusters: narrower tiles before any k split
     tiles = ((M + 255) // 256) * ((N + BN - 1) // BN)
@@ -1319,6 +1329,79 @@ class RowGroupGen:
         return src, launch
 
 
+class AttnGroupGen:
+    """A recognised attention run (attention.py) -> one launch of anvil::attn::attn_fused over a functor made of the two
+    products' own operand functors, the mask expression, and pointers to the dense row tensors."""
+
+    def __init__(self, gen: "ProgramGen", g: "at.AttnGroup"):
+        self.gen, self.g = gen, g
+
+    def generate(self, name: str):
+        gen, g = self.gen, self.g
+        k1, k2 = g.kernels[0], g.kernels[-1]
+        src = []
+        kg1 = KernelGen(gen, k1)
+        _, _, fe1 = kg1.gemm_functors(g.c1)
+        src += [kg1.comment("product 1 of a fused attention launch")] + kg1.tc_struct(g.c1, f"{name}_p1", fe1, True) + [""]
+        kg2 = KernelGen(gen, k2)
+        _, _, fe2 = kg2.gemm_functors(g.c2)
+        src += [kg2.comment("product 2 of a fused attention launch")] + kg2.tc_struct(g.c2, f"{name}_p2", fe2, True) + [""]
+        T, DH = at.T_TILE, at.DH_TILE
+
+        def base(root):
+            return f"((float *)(A + {gen.plan.offsets[root.id]}UL))"
+
+        def b(flag):
+            return "true" if flag else "false"
+        fn = "F_" + name
+        f = [f"// fused attention ({'forward' if g.mode == 0 else 'backward'}): " + " + ".join(k.name for k in g.kernels),
+             f"struct {fn} {{", "    char *__restrict__ A;",
+             f"    static constexpr int T = {T}, DH = {DH}, NBH = {g.nbh}, MODE = {g.mode};",
+             f"    static constexpr bool CAUSAL = {b(g.causal)}, STORE_R = {b(g.live['r'])}, STORE_E = {b(g.mode == 0 and g.live['e'])}, "
+             f"STORE_SUM = {b(g.mode == 0 and g.live['sum'])}, STORE_MAX = {b(g.mode == 0 and g.live['max'])};",
+             f"    static constexpr float ALPHA1 = {flit(g.c1.alpha)}, ALPHA2 = {flit(g.c2.alpha)};",
+             f"    __device__ __forceinline__ void a1(int i, int k, int bh, float (&v)[4]) const {{ {name}_p1{{A}}.a4(i, k, bh, v); }}",
+             f"    __device__ __forceinline__ void b1(int k, int j, int bh, float (&v)[4]) const {{ {name}_p1{{A}}.b4(k, j, bh, v); }}",
+             f"    __device__ __forceinline__ void b2(int k, int n, int bh, float (&v)[4]) const {{ {name}_p2{{A}}.b4(k, n, bh, v); }}",
+             f"    __device__ __forceinline__ void a1_touch(int i, int k, int bh) const {{ {name}_p1{{A}}.a_touch(i, k, bh); }}",
+             f"    __device__ __forceinline__ void b1_touch(int k, int j, int bh) const {{ {name}_p1{{A}}.b_touch(k, j, bh); }}",
+             f"    __device__ __forceinline__ void b2_touch(int k, int n, int bh) const {{ {name}_p2{{A}}.b_touch(k, n, bh); }}",
+             f"    __device__ __forceinline__ void epi(int i, int n, int bh, float acc) const {{ {name}_p2{{A}}.epi(i, n, bh, acc); }}",
+             f"    __device__ __forceinline__ float *r_row(int i, int bh) const {{ return {base(g.bufs['r'])} + ((long)bh * {T} + i) * {T}; }}",
+             f"    __device__ __forceinline__ float *e_row(int i, int bh) const {{ return {base(g.bufs['e'])} + ((long)bh * {T} + i) * {T}; }}",
+             f"    __device__ __forceinline__ float *sum_at(int i, int bh) const {{ return {base(g.bufs['sum'])} + (long)bh * {T} + i; }}"]
+        if g.mode == 0:
+            f.append(f"    __device__ __forceinline__ float *max_at(int i, int bh) const {{ return {base(g.bufs['max'])} + (long)bh * {T} + i; }}")
+            f.append(f"    __device__ __forceinline__ const float *p_row(int i, int bh) const {{ return r_row(i, bh); }}")
+            # the score from product 1's scaled accumulator: the elementwise kernel's expression with its load replaced
+            pk = g.post_kernel
+            kg = KernelGen(gen, pk)
+            names = dict(kg.names)
+            names[pk.domain[-2]], names[pk.domain[-1]] = "i", "j"
+            sc = Scope(kg, names, 1, None, "        ")
+            sc.preloaded = {(g.post_load.buf.root.id, g.post_load.off.key()): "acc"}
+            dec = kg.decode("(uint32_t)bh", pk.domain[:-2], names, "        ")
+            val = sc.ex([st for st in pk.stmts if isinstance(st, kir.Store)][0].value, 0)
+            f += ["    __device__ __forceinline__ float post(float acc, int i, int j, int bh) const {"] \
+                + ["    " + ln for ln in kg.pointer_decls()] + dec + sc.lines \
+                + [f"        return {val};", "    }"]
+        else:
+            f.append(f"    __device__ __forceinline__ float *max_at(int i, int bh) const {{ return nullptr; }}")
+            f.append(f"    __device__ __forceinline__ const float *p_row(int i, int bh) const {{ return {base(g.bufs['p'])} + ((long)bh * {T} + i) * {T}; }}")
+            f.append("    __device__ __forceinline__ float post(float acc, int i, int j, int bh) const { return acc; }")
+        f.append("};")
+        status = "(uint32_t *)(A + ANVIL_RT_STATUS_OFF)"
+        smem = f"anvil::attn::smem_bytes_att({T}, {DH})"
+        f += [f"__global__ void __launch_bounds__(anvil::attn::THREADS_ATT, 1) {name}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+              f"    anvil::attn::attn_fused<{fn}>({fn}{{A}}, {status});", "}"]
+        work = g.nbh * (T // 128)
+        launch = [f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({name}, "
+                  f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}",
+                  f"{name}<<<{min(work, 148)}, anvil::attn::THREADS_ATT, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);"]
+        note = f"attention {'fwd' if g.mode == 0 else 'bwd'} {g.nbh}x{T}x{T}x{DH}" + (" causal" if g.causal else "")
+        return "\n".join(src + f), launch, note
+
+
 class HGroupGen:
     """A horizontal group of contractions (see hfuse.py) -> one launch of the resident pair template over a functor
     that dispatches to the members' functors by tile column ("ncat") or by reduction block ("kcat")."""
@@ -1383,7 +1466,8 @@ class HGroupGen:
                   f"    __device__ __forceinline__ void epi_loads(int m, int n, int bt, float (&ld)[{L}]) const {{ {first}{{A}}.epi_loads(m, n, bt, ld); }}",
                   f"    __device__ __forceinline__ void epi2(int m, int n, int bt, float acc, const float (&ld)[{L}]) const {{ {first}{{A}}.epi2(m, n, bt, acc, ld); }}"]
         f.append("};")
-        BN, S, accs, work = pp_launch_params(M, N, K, 1)
+        seg_bn = 256 if kind != "ncat" or all(c.N % 256 == 0 for c in cs) else 128      # a tile never straddles two members
+        BN, S, accs, work = pp_launch_params(M, N, K, 1, seg_bn)
         AK = "true" if c0.a_kcontig else "false"
         BKC = "true" if ct._contig(c0.b, c0.kvars[-1]) else "false"
         status = "(uint32_t *)(A + ANVIL_RT_STATUS_OFF)"
@@ -1419,6 +1503,11 @@ class ProgramGen:
         self.seed = seed & 0xFFFFFFFF
         self.faults: list[str] = []
         self.scratch_bytes = 4
+        self.readers: dict = {}
+        for k in prog.kernels():
+            for r in k.reads():
+                self.readers.setdefault(r.id, set()).add(k.id)
+        self.causal_e: set = set()              # exp tensors written by causal fused attention (zero above the diagonal)
         self.plan = self.make_plan(0)
         self.kernel_index: dict[int, int] = {}
         self.kernels: list[kir.Kernel] = []
@@ -1441,10 +1530,6 @@ class ProgramGen:
         self.dead_roots: set = set()            # temporaries that live only in registers of a fused group (never stored)
         self.hot_units: list = []               # (launch-table index, note, [kernels]) of the training loop, in order
         self.record_units = False
-        self.readers: dict = {}
-        for k in prog.kernels():
-            for r in k.reads():
-                self.readers.setdefault(r.id, set()).add(k.id)
         self.host_read = self._host_reads()
 
     def make_plan(self, scratch_bytes: int):
@@ -1452,10 +1537,13 @@ class ProgramGen:
         loop conditions, checkpoints) or feeds (the step's inputs) keep their own memory, so they can be read between
         steps; row kernels that will run as one fused kernel count as one statement."""
         hot = an.hot_loop(self.prog)
-        keep = set(self._host_reads())
+        host = self._host_reads()
+        keep = set(host)
         if hot is not None:
             keep |= {b.root.id for b in an.input_producers(self.prog, hot)[1]}
-        runs = fused_runs
+        def runs(ks):
+            spans = at.find_attention(ks, self.readers, host, self.causal_e) if use_attention() else []
+            return fused_runs(ks, spans)
         return an.plan_arena(self.prog, scratch_bytes, share=os_environ("ANVIL_B200_ARENA", "shared") != "unshared",
                              fused_runs=runs, keep=keep)
 
@@ -1543,6 +1631,27 @@ class ProgramGen:
         return idx
 
     MAX_FAULT_CODES = 254
+
+    def add_attention(self, g) -> int:
+        """Launch-table index of the fused launch for a recognised attention run. Tensors that the fused kernel keeps in
+        tensor memory (scores, masked scores, row maxima / the three softmax-gradient temporaries) are never stored."""
+        key = ("a",) + tuple(k.id for k in g.kernels)
+        hit = self.groups.get(key)
+        if hit is not None:
+            return hit
+        idx = len(self.groups)
+        src, launch, note = AttnGroupGen(self, g).generate(f"a{idx}_{g.kernels[0].id}")
+        self.dead_roots |= {b.id for r, b in g.bufs.items() if not g.live[r]}
+        self.groups[key] = idx
+        self.group_src.append(src)
+        self.group_notes.append(note)
+        body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
+                "    uint32_t seed = anvil_rt_get_seed(rt);", "    uint32_t sdelta = 0;",
+                f"    RT(anvil_rt_prof_begin(rt, PROF_GROUP0 + {idx}));"] + ["    " + ln for ln in launch] \
+            + [f"    RT(anvil_rt_prof_end(rt, PROF_GROUP0 + {idx}));", "    return 0;"]
+        self.group_launchers.append(f"static int launch_group_{idx}(anvil_rt *rt) {{   // {' + '.join(k.name for k in g.kernels)}\n"
+                                    + "\n".join(body) + "\n}")
+        return idx
 
     def add_hgroup(self, kernels: list, kind: str) -> int:
         """Launch-table index of the fused launch for a horizontal group of contractions."""
@@ -1650,9 +1759,18 @@ class ProgramGen:
                 spans = rg.find_groups(run_kernels) if use_row_groups() else []
                 starts = {a: b for a, b in spans}
                 hstarts = {a: (b, kind) for a, b, kind in (hfuse.find_hgroups(run_kernels, tc_eligible_pp) if use_hgroups() else [])}
+                astarts = {a: (b, g) for a, b, g in (at.find_attention(run_kernels, self.readers, self.host_read, self.causal_e)
+                                                       if use_attention() else [])}
                 q = 0
                 while q < len(run_kernels):
-                    if q in hstarts:
+                    if q in astarts:
+                        end, g = astarts[q]
+                        gi = self.add_attention(g)
+                        calls.append(f"RT(launch_group_{gi}(rt));")
+                        if self.record_units:
+                            self.hot_units.append((("g", gi), self.group_notes[gi], g.kernels))
+                        q = end
+                    elif q in hstarts:
                         end, kind = hstarts[q]
                         ks = run_kernels[q:end]
                         gi = self.add_hgroup(ks, kind)
@@ -1870,7 +1988,7 @@ class ProgramGen:
         externs = [b for b in self.prog.roots() if b.kind in ("input", "output")]
         out = [f"// Generated by anvil-b200 from {self.prog.name}: sm_100a kernels over one device arena.",
                "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
-               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', '#include "anvil_gemm_sm100.cuh"', "",
+               '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', '#include "anvil_gemm_sm100.cuh"', '#include "anvil_attn_sm100.cuh"', "",
                "#define RT(call) do { if ((call) != 0) return 1; } while (0)", "",
                "// advances a loop counter that lives in the arena and returns its new value; on a failure the loop ends",
                "static long anvil_b200_advance(anvil_rt *rt, unsigned long off, int step, int *bad) {",

@@ -21,7 +21,7 @@ from __future__ import annotations
 from .. import kir
 from . import contraction as ct
 
-TILE_N = 256
+TILE_N = 128                   # outputs side by side must each be whole tiles wide (256-wide tiles when all are multiples of 256)
 BLOCK_K = 32
 
 
