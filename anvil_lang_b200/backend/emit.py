@@ -1065,9 +1065,13 @@ class KernelGen:
                     f"    {tile_fn}{S}{tile_tail}({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
-        launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
-                      f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
-        launch.append(f"{kname}<<<dim3({grid_x}, {grid_y}), {threads}, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
+        tma = pp and use_tma() and tma_kernel(self.gen, src, launch, kname, fn, c, c, AK, BKC, S, accs, BN, status,
+                                              f"(float *)(A + {self.gen.plan.scratch_off}UL)" if S > 1 else "nullptr",
+                                              f"dim3({grid_x}, {grid_y})", smem)
+        if not tma:
+            launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
+                          f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}")
+            launch.append(f"{kname}<<<dim3({grid_x}, {grid_y}), {threads}, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
         if S > 1:
             fb_ = max(1, min((M * N * NB + 255) // 256, MAX_BLOCKS))
             launch.append(self.launch_line(base, fb_, 256))
@@ -1138,6 +1142,36 @@ def pp_launch_params(M, N, K, NB, max_bn=256):
     S = max(S, (K + 4095) // 4096)       # one accumulation chain stays <= 4096 long (rounding, see the template's header)
     accs = 1 if (K + S - 1) // S <= 512 and BN == 256 else 2
     return BN, S, accs, tiles * NB * S
+
+
+def use_tma() -> bool:
+    """The TMA operand feed of the resident pair template is built and parity-tested but off by default: measured on a
+    B200 it is slower than the converters' own loads (16384 x 512 x 512: 72 us against 49 us). The stage ring holds three
+    66 KB stages (hi and lo tiles of both operands, 198 of 227 KB), so only one block's copy can be in flight while the
+    tensor core works on one stage and the converters make lo for the next, and a copy takes longer than a block's MMAs;
+    the load path keeps two blocks' operands in registers and asks L2 for four more. ANVIL_B200_TMA=1 turns it on."""
+    import os
+    return os.environ.get("ANVIL_B200_TMA", "0") == "1"
+
+
+def tma_operand(c, operand, row_vars):
+    """(root buffer, element offset, rows, row stride) when `operand` of contraction `c` can come by TMA: one plain load
+    of a row-major matrix read along k with 16-byte aligned rows — no prologue, no gather, no batch."""
+    if c.bvars or len(c.kvars) != 1 or operand.k != "load" or operand.dt != F32 or not operand.off.is_plain():
+        return None
+    off, kv = operand.off, c.kvars[0]
+    if off.coef(kv) != 1 or off.const % 4 or c.K % 4:
+        return None
+    live = [v for v in row_vars if v.extent > 1]
+    if not live or set(off.vars()) - set(live) - {kv}:
+        return None
+    stride = off.coef(live[-1])
+    if stride <= 0 or stride % 4 or stride < c.K:
+        return None
+    for v, s_ in zip(live, kir.row_major_strides([v.extent for v in live])):
+        if off.coef(v) != s_ * stride:
+            return None                              # the row vars do not flatten into one row index
+    return operand.buf.root, off.const, kir.prod(v.extent for v in live), stride
 
 
 def tc_min_flops() -> int:
@@ -1329,6 +1363,36 @@ class RowGroupGen:
         return src, launch
 
 
+def tma_kernel(gen, src: list, launch: list, kname: str, fn: str, ca, cb, AK, BKC, S, accs, BN, status, scratch, grid, smem) -> bool:
+    """When an operand of the resident pair template can come by TMA (`tma_operand`), adds a second __global__ function
+    `<kname>_tma` that takes the tensor maps as grid constants, and launch code that encodes the maps once per arena
+    (anvil_rt_tensor_map) and falls back to the plain kernel if that fails. `ca` / `cb`: the contractions whose A / B
+    operand the kernel reads (the same one, except for fused launches). Returns False when neither operand qualifies."""
+    a = tma_operand(ca, ca.a, ca.mvars) if AK == "true" else None
+    b = tma_operand(cb, cb.b, cb.nvars) if BKC == "true" and cb is not None else None
+    if a is None and b is None:
+        return False
+    mask = (1 if a else 0) | (2 if b else 0)
+    src += [f"__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(anvil::tc::PP_THREADS, 1) {kname}_tma(char *__restrict__ A, "
+            f"uint32_t sdelta, uint32_t seed_, const __grid_constant__ CUtensorMap tma, const __grid_constant__ CUtensorMap tmb) {{",
+            f"    anvil::tc::gemm_tc_pair_persistent<{fn}, {AK}, {BKC}, {S}, {accs}, {BN}, {mask}>({fn}{{A}}, {scratch}, {status}, &tma, &tmb);", "}"]
+    enc = []
+    if a:
+        root, const, rows, stride = a
+        enc.append(f"anvil_rt_tensor_map(rt, &tma_, {gen.plan.offsets[root.id] + 4 * const}UL, {rows}L, {ca.K}L, {stride}L, 128) == 0")
+    if b:
+        root, const, rows, stride = b
+        enc.append(f"anvil_rt_tensor_map(rt, &tmb_, {gen.plan.offsets[root.id] + 4 * const}UL, {rows}L, {cb.K}L, {stride}L, {BN // 2}) == 0")
+    launch += ["{ alignas(64) static CUtensorMap tma_, tmb_; static char *tm_base_ = nullptr; static bool tm_ok_ = false, attr_ = false;",
+               f"  if (!attr_) {{ cudaFuncSetAttribute({kname}, cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); "
+               f"cudaFuncSetAttribute({kname}_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }}",
+               f"  if (tm_base_ != A) {{ tm_ok_ = {' && '.join(enc)}; tm_base_ = A; }}        // the maps hold the arena's address",
+               f"  if (tm_ok_) {kname}_tma<<<{grid}, anvil::tc::PP_THREADS, {smem}, st>>>(A, sdelta, seed, tma_, tmb_);",
+               f"  else {kname}<<<{grid}, anvil::tc::PP_THREADS, {smem}, st>>>(A, sdelta, seed);",
+               "  anvil_rt_count_launches(rt, 1); }"]
+    return True
+
+
 class AttnGroupGen:
     """A recognised attention run (attention.py) -> one launch of anvil::attn::attn_fused over a functor made of the two
     products' own operand functors, the mask expression, and pointers to the dense row tensors."""
@@ -1479,9 +1543,12 @@ class HGroupGen:
             scratch = f"(float *)(A + {gen.plan.scratch_off}UL)"
         f += [f"__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(anvil::tc::PP_THREADS, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
               f"    anvil::tc::gemm_tc_pair_persistent<{name}, {AK}, {BKC}, {S}, {accs}, {BN}>({name}{{A}}, {scratch}, {status});", "}"]
-        launch = [f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
-                  f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}",
-                  f"{kname}<<<dim3({2 * min(work, 74)}, 1), anvil::tc::PP_THREADS, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);"]
+        launch = []
+        if not (kind == "ncat" and use_tma() and tma_kernel(gen, f, launch, kname, name, c0, None, AK, BKC, S, accs, BN, status, scratch,
+                                                          f"dim3({2 * min(work, 74)}, 1)", smem)):
+            launch = [f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
+                      f"cudaFuncAttributeMaxDynamicSharedMemorySize, (int){smem}); attr_ = true; }} }}",
+                      f"{kname}<<<dim3({2 * min(work, 74)}, 1), anvil::tc::PP_THREADS, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);"]
         if S > 1:
             f += [f"__global__ void __launch_bounds__(256) {kernel_name}_fin(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                   f"    anvil::gemm_split_finish<{name}, {S}>({name}{{A}}, (const float *)(A + {gen.plan.scratch_off}UL));", "}"]
@@ -1987,7 +2054,7 @@ class ProgramGen:
     def _assemble(self, main) -> str:
         externs = [b for b in self.prog.roots() if b.kind in ("input", "output")]
         out = [f"// Generated by anvil-b200 from {self.prog.name}: sm_100a kernels over one device arena.",
-               "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
+               "#include <cuda.h>", "#include <cuda_runtime.h>", "#include <math_constants.h>", "#include <stdint.h>", "#include <unistd.h>",
                '#include "anvil_cuda.h"', '#include "anvil_device.cuh"', '#include "anvil_gemm_simt.cuh"', '#include "anvil_gemm_sm100.cuh"', '#include "anvil_attn_sm100.cuh"', "",
                "#define RT(call) do { if ((call) != 0) return 1; } while (0)", "",
                "// advances a loop counter that lives in the arena and returns its new value; on a failure the loop ends",

@@ -113,8 +113,25 @@ struct TileMap {
     }
 };
 
+#ifndef ANVIL_TC_RAW_HI
+#define ANVIL_TC_RAW_HI 0
+#endif
 __device__ __forceinline__ void split_store(uint8_t *hi_tile, uint8_t *lo_tile, uint32_t off, const float (&v)[4]) {
     float4 hi, lo;
+#if ANVIL_TC_RAW_HI
+    {   // experiment: the hi tile holds the raw f32 (the tensor core reads its top 19 bits); lo against truncation (1) or rounding (2)
+        float h[4];
+        for (int z = 0; z < 4; z++) {
+            if (ANVIL_TC_RAW_HI == 1) h[z] = __uint_as_float(__float_as_uint(v[z]) & 0xFFFFE000u);
+            else { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[z])); h[z] = __uint_as_float(u); }
+        }
+        hi = make_float4(v[0], v[1], v[2], v[3]);
+        lo = make_float4(v[0] - h[0], v[1] - h[1], v[2] - h[2], v[3] - h[3]);
+        *reinterpret_cast<float4 *>(hi_tile + off) = hi;
+        *reinterpret_cast<float4 *>(lo_tile + off) = lo;
+        return;
+    }
+#endif
     hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
     hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xFFFFE000u); lo.y = v[1] - hi.y;
     hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xFFFFE000u); lo.z = v[2] - hi.z;
@@ -700,6 +717,35 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
                  ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
 
+// ---- TMA (cp.async.bulk.tensor) for operands that are plain row-major matrices read along k
+// A 2-d tensor map {k, rows} with a box of {4 floats, R rows} brings one 16-byte column of R rows — exactly one k-chunk
+// of the K-major no-swizzle operand layout, rows 16 bytes apart. Eight such copies fill a 32-wide k block. The raw f32
+// words ARE the hi operand: a kind::tf32 MMA reads the upper 19 bits of each word and ignores the low 13 mantissa bits,
+// which is the truncation the converters otherwise do by hand; they then only read the tile back and write lo = x - hi.
+// No cluster multicast: each CTA of a pair loads its own rows into its own shared memory.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// lo = x - trunc_tf32(x) for a ROWS x 32 tile the TMA wrote densely (k-chunk c at c * ROWS * 16); lo goes to the padded layout
+template <int ROWS>
+__device__ __forceinline__ void lo_from_raw_tile(const uint8_t *hi_tile, uint8_t *lo_tile, uint32_t lbo, int t) {
+#pragma unroll
+    for (int p = 0; p < ROWS / 32; p++) {
+        const int row = t % ROWS, kc = t / ROWS + (CONV_THREADS / ROWS) * p;        // consecutive lanes on consecutive rows: no bank conflicts
+        const float4 x = *reinterpret_cast<const float4 *>(hi_tile + kc * (ROWS * 16) + row * 16);
+        float4 lo;
+        lo.x = x.x - __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+        lo.y = x.y - __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+        lo.z = x.z - __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+        lo.w = x.w - __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+        *reinterpret_cast<float4 *>(lo_tile + kc * lbo + row * 16) = lo;
+    }
+}
+
 // Launched with cluster dimensions (2, 1, 1): blockIdx.x >> 1 is the tile, %cluster_ctarank the half.
 template <class F, bool AK, bool BKC, int BN, int SPLIT>
 __device__ __forceinline__ void gemm_tc_pair_tile(const F &f, float *__restrict__ partial, uint32_t *status) {
@@ -895,8 +941,11 @@ __host__ __device__ constexpr uint32_t pp_smem_bytes(int bn = 256) {
 
 // BN = 256, 128 or 64 columns per tile (narrow outputs: the attention products with a 64-wide head). With BN <= 128
 // two accumulator pairs fit, so ACCS = 2 is double-buffered as well.
-template <class F, bool AK, bool BKC, int SPLIT, int ACCS, int BN = 256>
-__device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__restrict__ partial, uint32_t *status) {
+// TMA: bit 0 — the A operand comes by TMA through the tensor map `tma` ({K, M} f32, box {4, 128}); bit 1 — B through `tmb`
+// ({K, N}, box {4, BN / 2}). Both need the operand to be a plain row-major matrix read along k with 16-byte aligned rows.
+template <class F, bool AK, bool BKC, int SPLIT, int ACCS, int BN = 256, int TMA = 0>
+__device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__restrict__ partial, uint32_t *status,
+                                                        const void *tma = nullptr, const void *tmb = nullptr) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int M = F::M, N = F::N, K = F::K;
     constexpr int BH = BN / 2;
@@ -923,6 +972,10 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
     auto tfull = [&](int b) { return bar0 + 8u * (2 * NST + b); };
     auto tempty = [&](int b) { return bar0 + 8u * (2 * NST + 2 + b); };
     const uint32_t alldone = smem_u32(smem + BAR_OFF + 112);                     // every MMA of this cluster has completed
+    auto raw_full = [&](int s) { return smem_u32(smem + BAR_OFF + 120) + 8u * s; };   // this CTA's TMA copies of stage s have landed
+    constexpr bool TMA_A = (TMA & 1) != 0, TMA_B = (TMA & 2) != 0;
+    constexpr uint32_t LBO_AH = TMA_A ? (uint32_t)BM * 16u : LBO_A, LBO_BH = TMA_B ? (uint32_t)BH * 16u : LBO_B;   // hi tiles from TMA are dense
+    static_assert(!TMA || F::NB == 1, "tensor maps describe one matrix");
 
     // One work item: which rows / columns / k range. All roles walk the same sequence w = cid, cid + ncl, ...
     struct Item { int m0, n0, nb0, bt, sp, k_begin, k_end, nkb; };
@@ -942,6 +995,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         for (int s = 0; s < NST; s++) { mbar_init(full(s), 2 * 8); mbar_init(empty(s), 1); }
         for (int b = 0; b < 2; b++) { mbar_init(tfull(b), 1); mbar_init(tempty(b), 2 * PP_EPI_WARPS); }
         mbar_init(alldone, 1);
+        for (int s = 0; s < NST; s++) mbar_init(raw_full(s), 1);
         *failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -1011,21 +1065,36 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         float va[BM / 32][4], vb[BH / 32][4];
         auto fetch = [&](const Item &it, int kb) {
             const int k0 = it.k_begin + kb * BK;
+            if (!TMA_A) {
 #pragma unroll
-            for (int p = 0; p < BM / 32; p++) {
-                int row, kc;
-                TileMap<AK, BM>::at(tc, p, row, kc);
-                const int m = it.m0 + row, k = k0 + kc * 4;
-                if (m < M && k < it.k_end) f.a4(m, k, it.bt, va[p]);
-                else { va[p][0] = va[p][1] = va[p][2] = va[p][3] = 0.0f; }
+                for (int p = 0; p < BM / 32; p++) {
+                    int row, kc;
+                    TileMap<AK, BM>::at(tc, p, row, kc);
+                    const int m = it.m0 + row, k = k0 + kc * 4;
+                    if (m < M && k < it.k_end) f.a4(m, k, it.bt, va[p]);
+                    else { va[p][0] = va[p][1] = va[p][2] = va[p][3] = 0.0f; }
+                }
             }
+            if (!TMA_B) {
 #pragma unroll
-            for (int p = 0; p < BH / 32; p++) {
-                int row, kc;
-                TileMap<BKC, BH>::at(tc, p, row, kc);
-                const int n = it.nb0 + row, k = k0 + kc * 4;
-                if (n < N && k < it.k_end) f.b4(k, n, it.bt, vb[p]);
-                else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+                for (int p = 0; p < BH / 32; p++) {
+                    int row, kc;
+                    TileMap<BKC, BH>::at(tc, p, row, kc);
+                    const int n = it.nb0 + row, k = k0 + kc * 4;
+                    if (n < N && k < it.k_end) f.b4(k, n, it.bt, vb[p]);
+                    else { vb[p][0] = vb[p][1] = vb[p][2] = vb[p][3] = 0.0f; }
+                }
+            }
+        };
+        // The TMA copies of block (it, kb) into stage s: eight 16-byte columns per operand; rows or k beyond the matrix read as zeros
+        auto tma_issue = [&](const Item &it, int kb, int s) {
+            const int k0 = it.k_begin + kb * BK;
+            const uint32_t st = smem_u32(smem + s * STAGE);
+            mbar_expect_tx(raw_full(s), (TMA_A ? BM * 128u : 0u) + (TMA_B ? BH * 128u : 0u));
+#pragma unroll
+            for (int c = 0; c < BK / 4; c++) {
+                if (TMA_A) tma_load_2d(st + c * (BM * 16), tma, k0 + 4 * c, it.m0, raw_full(s));
+                if (TMA_B) tma_load_2d(st + 2 * TA + c * (BH * 16), tmb, k0 + 4 * c, it.nb0, raw_full(s));
             }
         };
         // L2 prefetch of a later block of the same item: one 128-byte line per 32 k of a row (operand contiguous
@@ -1078,21 +1147,31 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
             const uint32_t ph = (uint32_t)(n / NST) & 1u;
             if (!mbar_wait(empty(s), ph ^ 1)) { *failed = 1; break; }
             uint8_t *st = smem + s * STAGE;
+            if (TMA && (warp & 7) == 0 && lane == 0) tma_issue(it, kb, s);       // one thread of the group starts this block's copies
+            if (!TMA_A) {
 #pragma unroll
-            for (int p = 0; p < BM / 32; p++) {
-                int row, kc;
-                TileMap<AK, BM>::at(tc, p, row, kc);
-                split_store(st, st + TA, kc * LBO_A + row * 16, va[p]);
+                for (int p = 0; p < BM / 32; p++) {
+                    int row, kc;
+                    TileMap<AK, BM>::at(tc, p, row, kc);
+                    split_store(st, st + TA, kc * LBO_A + row * 16, va[p]);
+                }
             }
+            if (!TMA_B) {
 #pragma unroll
-            for (int p = 0; p < BH / 32; p++) {
-                int row, kc;
-                TileMap<BKC, BH>::at(tc, p, row, kc);
-                split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
+                for (int p = 0; p < BH / 32; p++) {
+                    int row, kc;
+                    TileMap<BKC, BH>::at(tc, p, row, kc);
+                    split_store(st + 2 * TA, st + 2 * TA + TB, kc * LBO_B + row * 16, vb[p]);
+                }
             }
             kb += G;
             settle();
             if (w < WORK) { fetch(it, kb); touch_next(); }
+            if (TMA) {                                                           // the raw tiles have landed: they are the hi operand; make lo
+                if (!mbar_wait(raw_full(s), ph)) { *failed = 1; break; }
+                if (TMA_A) lo_from_raw_tile<BM>(st, st + TA, LBO_A, tc);
+                if (TMA_B) lo_from_raw_tile<BH>(st + 2 * TA, st + 2 * TA + TB, LBO_B, tc);
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(full_leader0 + 8u * s);
@@ -1132,8 +1211,8 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
                     const uint32_t a_hi = base + s * STAGE, a_lo = a_hi + TA, b_hi = a_hi + 2 * TA, b_lo = b_hi + TB;
 #pragma unroll
                     for (int j = 0; j < BK / 8; j++) {
-                        const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_A, LBO_A), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
-                        const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B, LBO_B), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
+                        const uint64_t dah = smem_desc(a_hi + 2 * j * LBO_AH, LBO_AH), dal = smem_desc(a_lo + 2 * j * LBO_A, LBO_A);
+                        const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_BH, LBO_BH), dbl = smem_desc(b_lo + 2 * j * LBO_B, LBO_B);
                         if (ACCS == 2) {
                             mma_tf32_pair(acc + BN, dah, dbl, IDESC, (kb | j) ? 1u : 0u);
                             mma_tf32_pair(acc + BN, dal, dbh, IDESC, 1u);

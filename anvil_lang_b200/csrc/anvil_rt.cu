@@ -809,6 +809,39 @@ extern "C" int anvil_rt_time_launch(anvil_rt *rt, anvil_launch_fn launch, int in
     return 0;
 }
 
+// ---------------------------------------------------------------------------- tensor maps
+// A TMA descriptor of a row-major f32 matrix inside the arena, for the contraction templates' k-major operand feed:
+// dimensions {cols, rows}, row stride in elements, box {4 columns, box_rows rows} (one 16-byte column of the operand
+// tile per copy), no swizzle, zeros outside the matrix. cuTensorMapEncodeTiled is looked up through the runtime API,
+// so the library does not link against the driver. Returns 0, or 1 with the reason in anvil_rt_last_error (the caller
+// then launches the variant without TMA).
+#include <cuda.h>
+extern "C" int anvil_rt_tensor_map(anvil_rt *rt, void *map_out, size_t off, long rows, long cols, long row_stride, int box_rows) {
+    typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess)
+            return fail(rt, "anvil: cuTensorMapEncodeTiled is not available");
+        encode = (encode_fn)fn;
+    }
+    if (in_range(rt, off, 4 * (size_t)((rows - 1) * row_stride + cols))) return 1;
+    if (off % 16 || row_stride % 4 || cols % 4 || box_rows < 1 || box_rows > 256)
+        return fail(rt, "anvil: operand is not 16-byte aligned for a tensor map");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_stride * 4};
+    const cuuint32_t box[2] = {4, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode((CUtensorMap *)map_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, rt->arena + off, dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(rt, "anvil: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return 0;
+}
+
 // ---------------------------------------------------------------------------- collective
 extern "C" void anvil_rt_set_allreduce(anvil_rt *rt, anvil_allreduce_fn fn, void *user) {
     rt->allreduce = fn;

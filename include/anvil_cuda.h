@@ -171,6 +171,12 @@ int anvil_rt_timer_end(anvil_rt *rt, float *milliseconds);    /* synchronises on
 typedef int (*anvil_launch_fn)(anvil_rt *, int);
 int anvil_rt_time_launch(anvil_rt *rt, anvil_launch_fn launch, int index, int repeats, float *milliseconds);
 
+/* ---- TMA descriptors for the contraction templates (no reference counterpart: its kernels read operands with plain
+ * loads, anvil/backend/cuda.py:282-313). Writes a 128-byte CUtensorMap for the row-major f32 matrix of `rows` x `cols`
+ * elements at arena offset `off` (rows `row_stride` elements apart; offset, stride and cols multiples of 16 bytes) with a
+ * box of 4 columns x `box_rows` rows, zeros outside the matrix, into `map_out` (64-byte aligned host memory). */
+int anvil_rt_tensor_map(anvil_rt *rt, void *map_out, size_t off, long rows, long cols, long row_stride, int box_rows);
+
 /* ---- the data-parallel collective (no reference counterpart: the reference is single-device).
  * Sums `count` f32 values at arena offset `off` over all ranks, in place, stream-ordered. The
  * collective itself is supplied by the host program (NCCL through torch.distributed in this repo). */

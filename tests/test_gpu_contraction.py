@@ -108,3 +108,43 @@ def test_full_size_transformer_products(case, variant):
     err, note = run_case(case, tc=variant)
     assert note.startswith("gemm tc"), note
     assert err < 3e-5, (err, note)
+
+
+def test_tma_operand_feed():
+    """Plain row-major operands read along k arrive by TMA (cp.async.bulk.tensor, one 16-byte column of the tile per copy,
+    no multicast) and serve as the hi operand as they are; the converters only make the lo tile. The tensor map must
+    encode for the shape and the product must match float64. Both variants are timed on the same data and the times
+    printed: the feed is opt-in (ANVIL_B200_TMA=1) because with three 66 KB stages only one copy is in flight and it
+    measured slower (72 us against 49 us) than the converters' own register-prefetched loads."""
+    import ctypes
+    case = BIG_CASES[3]                                  # 16384 x 512 x 512, both operands read along k, += into C
+    times = {}
+    for tma in ("1", "0"):
+        os.environ["ANVIL_B200_TMA"] = tma
+        os.environ["ANVIL_B200_TC"] = "pp"
+        try:
+            prog, kern, A, B, C, bias_b = contraction_program(*case)
+            dp = DeviceProgram(prog, graphs=False)
+        finally:
+            os.environ.pop("ANVIL_B200_TMA", None)
+            os.environ.pop("ANVIL_B200_TC", None)
+        assert ("_tma<<<" in dp.source) == (tma == "1")
+        if tma == "1":
+            buf = (ctypes.c_char * 192)()
+            at = (ctypes.addressof(buf) + 63) // 64 * 64
+            rc = dp.rtlib.anvil_rt_tensor_map(dp.rt, ctypes.c_void_p(at), dp.plan.off(A), 16384, 512, 512, 128)
+            assert rc == 0, dp.rtlib.anvil_rt_last_error(dp.rt)
+        rng = np.random.default_rng(3)
+        a = rng.standard_normal(A.numel, dtype=np.float32)
+        b = rng.standard_normal(B.numel, dtype=np.float32)
+        c0 = rng.standard_normal(C.numel, dtype=np.float32)
+        dp.write(A, a); dp.write(B, b); dp.write(C, c0)
+        dp.launch(kern)
+        dp.check_faults()
+        got = dp.read(C).astype(np.float64)
+        want = contraction_reference(a, b, c0, None, *case[:3], 1, False, True, False, False, 1.0, True, False)
+        assert np.abs(got - want).max() / np.abs(want).max() < 1e-5
+        times[tma] = min(dp.time_kernel(kern, 5) for _ in range(3))
+        dp.close()
+    print(f"16384x512x512 +=: TMA feed {times['1'] * 1e3:.1f} us, converter loads {times['0'] * 1e3:.1f} us")
+    assert times["1"] <= 3 * times["0"]
