@@ -51,6 +51,7 @@ def _stamp(paths) -> str:
 
 def runtime_sources():
     return [os.path.join(CSRC, "anvil_rt.cu"), os.path.join(CSRC, "anvil_colsum_static.cu"), os.path.join(CSRC, "anvil_selftest.cu"),
+            os.path.join(CSRC, "anvil_comm.cu"),
             os.path.join(CSRC, "anvil_gemm_sm100.cuh"), os.path.join(CSRC, "anvil_rng.h"),
             os.path.join(INCLUDE, "anvil_cuda.h")]
 
@@ -65,7 +66,7 @@ def build_runtime(force: bool = False) -> str:
         return RT_LIB
     cus = [p for p in srcs if p.endswith(".cu")]
     cmd = [nvcc(), "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS,
-           "-I", INCLUDE, "-I", CSRC, "-o", RT_LIB, *cus, "-lz"]
+           "-I", INCLUDE, "-I", CSRC, "-o", RT_LIB, *cus, "-lz", "-lpthread", "-ldl"]
     _run(cmd)
     with open(stamp_file, "w") as f:
         f.write(stamp)
@@ -123,6 +124,7 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_profile_get": (I, [P, I, c.POINTER(c.c_double), c.POINTER(L)]),
         "anvil_rt_h2d": (I, [P, Z, P, Z]), "anvil_rt_d2h": (I, [P, P, Z, Z]),
         "anvil_rt_h2d_async": (I, [P, Z, P, Z]), "anvil_rt_d2h_async": (I, [P, P, Z, Z]),
+        "anvil_rt_h2d_staged": (I, [P, Z, P, Z]), "anvil_rt_d2h_staged": (I, [P, P, Z, Z]),
         "anvil_rt_zero": (I, [P, Z, Z]), "anvil_rt_sync": (I, [P]),
         "anvil_rt_host_alloc": (P, [Z]), "anvil_rt_host_free": (None, [P]),
         "anvil_rt_set_i32": (I, [P, Z, c.c_int32]), "anvil_rt_set_f32": (I, [P, Z, c.c_float]),
@@ -141,6 +143,8 @@ def load_runtime() -> ctypes.CDLL:
         "anvil_rt_timer_begin": (I, [P]), "anvil_rt_timer_end": (I, [P, c.POINTER(c.c_float)]),
         "anvil_rt_time_launch": (I, [P, P, I, I, c.POINTER(c.c_float)]),
         "anvil_rt_set_allreduce": (None, [P, P, P]), "anvil_rt_allreduce": (I, [P, Z, L]),
+        "anvil_rt_comm_unique_id": (I, [P, Z]), "anvil_rt_comm_init": (I, [P, I, I, P, Z]),
+        "anvil_rt_comm_nranks": (I, [P]), "anvil_rt_comm_destroy": (I, [P]),
         "anvil_colsum_f32_static": (I, [P, L, L, P, P]),
         "anvil_rt_selftest_wait": (I, [P, c.c_longlong, c.POINTER(U), c.POINTER(c.c_longlong)]),
         "anvil_rt_tensor_map": (I, [P, P, Z, L, L, L, I]),

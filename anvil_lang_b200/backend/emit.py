@@ -2118,12 +2118,12 @@ class ProgramGen:
             for b in externs:
                 if b.kind == "input":
                     if b.nbytes:                     # an empty array has nothing to copy (its host pointer may be dangling)
-                        out.append(f"    if (anvil_{b.name}) RT(anvil_rt_h2d_async(rt, {self.off(b)}, anvil_{b.name}, {b.nbytes}UL));")
+                        out.append(f"    if (anvil_{b.name}) RT(anvil_rt_h2d_staged(rt, {self.off(b)}, anvil_{b.name}, {b.nbytes}UL));")
             out.append("    RT(anvil_b200_main(rt, 0));")
             for b in externs:
                 if b.kind == "output":
                     if b.nbytes:
-                        out.append(f"    if (anvil_{b.name}) RT(anvil_rt_d2h_async(rt, anvil_{b.name}, {self.off(b)}, {b.nbytes}UL));")
+                        out.append(f"    if (anvil_{b.name}) RT(anvil_rt_d2h_staged(rt, anvil_{b.name}, {self.off(b)}, {b.nbytes}UL));")
             out += ["    return anvil_rt_sync(rt);", "}"]
         return "\n".join(out) + "\n"
 

@@ -17,6 +17,7 @@
 
 #include <map>
 #include <string>
+#include <thread>
 #include <vector>
 
 struct anvil_graph {
@@ -54,6 +55,8 @@ struct anvil_rt {
     std::map<int, std::pair<double, long>> prof;      // slot -> (milliseconds, calls)
     std::vector<int> prof_order;    // slots in the order they first ran
     cudaEvent_t pe0 = nullptr, pe1 = nullptr;
+    char *stage[2] = {nullptr, nullptr};        // pinned staging buffers for large copies from / to pageable host memory
+    cudaEvent_t stage_ev[2] = {nullptr, nullptr};
 };
 
 static double now_seconds() {
@@ -99,10 +102,12 @@ extern "C" void anvil_rt_destroy(anvil_rt *rt) {
     if (!rt) return;
     cudaSetDevice(rt->device);
     if (rt->stream) cudaStreamSynchronize(rt->stream);
+    anvil_rt_comm_destroy(rt);
     for (auto &g : rt->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
     if (rt->arena) cudaFree(rt->arena);
     if (rt->ev0) { cudaEventDestroy(rt->ev0); cudaEventDestroy(rt->ev1); }
     if (rt->pe0) { cudaEventDestroy(rt->pe0); cudaEventDestroy(rt->pe1); }
+    for (int i = 0; i < 2; i++) { if (rt->stage[i]) cudaFreeHost(rt->stage[i]); if (rt->stage_ev[i]) cudaEventDestroy(rt->stage_ev[i]); }
     if (rt->stream && rt->own_stream) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -170,6 +175,62 @@ extern "C" int anvil_rt_d2d_async(anvil_rt *rt, size_t off, const void *src_devi
 extern "C" int anvil_rt_d2h_async(anvil_rt *rt, void *dst, size_t off, size_t bytes) {
     if (in_range(rt, off, bytes)) return 1;
     CK(rt, cudaMemcpyAsync(dst, rt->arena + off, bytes, cudaMemcpyDeviceToHost, rt->stream));
+    return 0;
+}
+// Large copies between the arena and PAGEABLE host memory (the arrays an `anvil.function` caller hands over): a plain
+// cudaMemcpyAsync stages them through the driver's own bounce buffer at about 5 GB/s. Here the copy is cut into 8 MiB
+// chunks that go through two pinned buffers: host threads fill (or drain) one while the DMA engine moves the other.
+static const size_t STAGE_BYTES = 8u << 20;
+static const int STAGE_THREADS = 4;
+static void parallel_copy(char *dst, const char *src, size_t n) {
+    if (n < (1u << 20)) { memcpy(dst, src, n); return; }
+    std::thread th[STAGE_THREADS];
+    const size_t part = (n / STAGE_THREADS + 63) / 64 * 64;
+    for (int i = 0; i < STAGE_THREADS; i++) {
+        const size_t lo = (size_t)i * part, hi = lo + part < n ? lo + part : n;
+        th[i] = std::thread([=] { if (lo < hi) memcpy(dst + lo, src + lo, hi - lo); });
+    }
+    for (auto &t : th) t.join();
+}
+static int ensure_stage(anvil_rt *rt) {
+    for (int i = 0; i < 2; i++) {
+        if (!rt->stage[i]) CK(rt, cudaMallocHost((void **)&rt->stage[i], STAGE_BYTES));
+        if (!rt->stage_ev[i]) CK(rt, cudaEventCreateWithFlags(&rt->stage_ev[i], cudaEventDisableTiming));
+    }
+    return 0;
+}
+extern "C" int anvil_rt_h2d_staged(anvil_rt *rt, size_t off, const void *src, size_t bytes) {
+    if (in_range(rt, off, bytes)) return 1;
+    if (bytes < 2 * STAGE_BYTES) return anvil_rt_h2d_async(rt, off, src, bytes);
+    if (ensure_stage(rt)) return 1;
+    int i = 0;
+    for (size_t done = 0; done < bytes; done += STAGE_BYTES, i ^= 1) {
+        const size_t n = bytes - done < STAGE_BYTES ? bytes - done : STAGE_BYTES;
+        CK(rt, cudaEventSynchronize(rt->stage_ev[i]));                  // the copy that last used this buffer has finished
+        parallel_copy(rt->stage[i], (const char *)src + done, n);
+        CK(rt, cudaMemcpyAsync(rt->arena + off + done, rt->stage[i], n, cudaMemcpyHostToDevice, rt->stream));
+        CK(rt, cudaEventRecord(rt->stage_ev[i], rt->stream));
+    }
+    return 0;
+}
+// The result is in `dst` when the call returns (unlike anvil_rt_d2h_async).
+extern "C" int anvil_rt_d2h_staged(anvil_rt *rt, void *dst, size_t off, size_t bytes) {
+    if (in_range(rt, off, bytes)) return 1;
+    if (bytes < 2 * STAGE_BYTES) { if (anvil_rt_d2h_async(rt, dst, off, bytes)) return 1; return anvil_rt_sync(rt); }
+    if (ensure_stage(rt)) return 1;
+    const size_t chunks = (bytes + STAGE_BYTES - 1) / STAGE_BYTES;
+    for (size_t c = 0; c <= chunks; c++) {                              // chunk c is copied out while chunk c - 1 is drained
+        if (c < chunks) {
+            const size_t n = bytes - c * STAGE_BYTES < STAGE_BYTES ? bytes - c * STAGE_BYTES : STAGE_BYTES;
+            CK(rt, cudaMemcpyAsync(rt->stage[c & 1], rt->arena + off + c * STAGE_BYTES, n, cudaMemcpyDeviceToHost, rt->stream));
+            CK(rt, cudaEventRecord(rt->stage_ev[c & 1], rt->stream));
+        }
+        if (c > 0) {
+            const size_t p = c - 1, n = bytes - p * STAGE_BYTES < STAGE_BYTES ? bytes - p * STAGE_BYTES : STAGE_BYTES;
+            CK(rt, cudaEventSynchronize(rt->stage_ev[p & 1]));
+            parallel_copy((char *)dst + p * STAGE_BYTES, rt->stage[p & 1], n);
+        }
+    }
     return 0;
 }
 extern "C" int anvil_rt_zero(anvil_rt *rt, size_t off, size_t bytes) {

@@ -129,7 +129,7 @@ def run_data_parallel(prog, args, argv) -> int:
         devprog = DeviceProgram(sharded, seed=args.seed, device=dev, graphs=not args.no_graphs)
         try:
             devprog.set_rank(rank)
-            _dp.attach(devprog, dev)
+            _dp.attach_native(devprog, rank, world)
             code, _ = devprog.run(capture=rank != 0)
             if code == 1 and devprog.error and rank == 0:
                 print(devprog.error, file=sys.stderr)

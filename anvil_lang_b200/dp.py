@@ -15,7 +15,8 @@ the single-GPU program: rank r of G runs the program compiled for the local batc
      rides along), so parameters stay bit-identical on every rank.
 
 Parameter initialisation and the shuffle are untouched: same seed, same bits on every rank.
-The collective itself is NCCL through `torch.distributed` on the program's stream (`attach`).
+The collective itself is NCCL inside the runtime (`attach_native`, csrc/anvil_comm.cu), ordered on the program's stream;
+`attach` routes it through a host program's `torch.distributed` group instead.
 """
 from __future__ import annotations
 
@@ -238,10 +239,55 @@ def shard(prog: kir.Program, world: int) -> kir.Program:
 _keep = []          # ctypes callbacks must outlive the programs that hold them
 
 
+def attach_native(devprog, rank: int, world: int, id_file: str | None = None, timeout_s: float = 120.0):
+    """Joins the runtime's own NCCL communicator (csrc/anvil_comm.cu): the program's `kir.AllReduce` becomes
+    ncclAllReduce(sum, f32) in place on the arena's gradient bucket, ordered on the program's stream — no Python, no
+    torch in the step. Only the 128-byte communicator id has to travel from rank 0 to the others once: through the
+    default `torch.distributed` group when one is initialised, else through `id_file` (rank 0 writes it, the others wait
+    for it), which is all a C host would need."""
+    import ctypes
+    import os
+    import time
+    buf = (ctypes.c_char * 128)()
+    use_file = id_file is not None
+    dist = None
+    if not use_file:
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            raise RuntimeError("anvil: no process group and no id file to hand the communicator id around")
+    if rank == 0:
+        if devprog.rtlib.anvil_rt_comm_unique_id(buf, 128) != 0:
+            raise RuntimeError("anvil: NCCL is not available (libnccl.so.2 could not be loaded)")
+        if use_file:
+            tmp = id_file + ".tmp"
+            with open(tmp, "wb") as f:
+                f.write(bytes(buf))
+            os.replace(tmp, id_file)
+    if use_file and rank != 0:
+        t0 = time.time()
+        while not os.path.exists(id_file):
+            if time.time() - t0 > timeout_s:
+                raise TimeoutError(f"anvil: rank 0 never wrote the communicator id to {id_file}")
+            time.sleep(0.01)
+        with open(id_file, "rb") as f:
+            raw = f.read()
+        ctypes.memmove(buf, raw, 128)
+    if not use_file:
+        box = [bytes(buf) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ctypes.memmove(buf, box[0], 128)
+    devprog._check(devprog.rtlib.anvil_rt_comm_init(devprog.rt, rank, world, buf, 128))
+    n = devprog.rtlib.anvil_rt_comm_nranks(devprog.rt)
+    if n != world:
+        raise RuntimeError(f"anvil: the communicator has {n} ranks, expected {world}")
+    return n
+
+
 def attach(devprog, device: int):
     """Binds a sharded `DeviceProgram` to the default `torch.distributed` process group (NCCL): the
     program runs on a torch-owned stream, and its `kir.AllReduce` becomes `dist.all_reduce(SUM)` on
-    a tensor that aliases the arena's gradient bucket (in place, no staging copy)."""
+    a tensor that aliases the arena's gradient bucket (in place, no staging copy). Kept for hosts that already own a
+    process group and want its collective; `attach_native` is what `bench.py` and the command line use."""
     import ctypes
 
     import torch

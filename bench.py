@@ -31,10 +31,10 @@ WORKLOADS = {
     "c1": ("c1_mlp_sgd", 64, "MLP 784-128-10, f32, cross_entropy, SGD lr 0.1, batch 64"),
 }
 L2_BYTES = 126 << 20
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under
-# profiles/ (gemm_tc_pp_16384x512x2048.md, c5_transformer_step_launches.md), keyed by the kernel's strategy note
-NCU_TRAFFIC = {"gemm tc 1x16384x512x2048": 141.8e6 + 13.9e6, "gemm tc 1x512x512x16384": 67.3e6 + 5.0e6,
-               "gemm tc 1x16384x512x512": 34.6e6 + 0.6e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel templates, from ncu captures of single launches
+# (the heaviest shape of the template in the transformer step; summaries of the captures are kept with the project's
+# profiles). Keyed by template.
+NCU_TRAFFIC_PER_LAUNCH = {"gemm tc": 141.8e6 + 13.9e6}
 
 
 def load_program(name):
@@ -118,8 +118,88 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(name, batch, budget_s=20.0):
-    """The CPU baseline: the oracle (NumPy restatement of the reference interpreter, reduction bodies
+REDUCED = {          # whole training steps the reference interpreter finishes in seconds: the same program at a reduced size
+    "c5_transformer": {"BATCH": 2, "LAYERS": 2, "D": 128, "HEADS": 2, "T": 256},
+    "c3_mlp_adam": {}, "c4_cnn_sgd": {}, "c1_mlp_sgd": {},
+}
+
+
+def step_flops(prog):
+    from anvil_lang_b200 import kir
+    from anvil_lang_b200.backend import analysis as an
+    hot = an.hot_loop(prog)
+    return sum(an.kernel_flops(st.kernel) for st in hot.body.stmts if isinstance(st, kir.KernelStmt))
+
+
+class ReferenceSteps:
+    """The reference implementation itself (oracle/_ref: its front end and its NumPy interpreter, anvil/interp.py) running
+    whole training steps of a configuration on the host. Configurations whose full-size step takes hours on the
+    interpreter (the transformer: 8969 s per step, measured when the golden losses were made) run at a reduced size —
+    same program text, smaller constants — and the time is scaled to the full size by the FLOP count of a step."""
+
+    def __init__(self, name):
+        ref = os.path.join(ROOT, "oracle", "_ref")
+        if not os.path.isdir(os.path.join(ref, "anvil")):
+            raise ImportError("oracle/_ref is absent")
+        sys.path.insert(0, ref)
+        sys.dont_write_bytecode = True
+        os.environ.setdefault("ANVIL_CACHE", tempfile.mkdtemp(prefix="anvil_cache_"))
+        from anvil import ir
+        from anvil.driver import compile_file
+        from anvil.interp import Interpreter
+        from anvil_lang_b200 import kir
+        from anvil_lang_b200.backend import analysis as an
+        consts = REDUCED[name]
+        c = compile_file(os.path.join(ROOT, "anvil_lang_b200", "programs", f"{name}.anvil"), consts=consts or None)
+        k = kir.from_anvil(c.program, name)
+        hot = an.hot_loop(k)
+        self.scale = step_flops(load_program(name)) / step_flops(k)
+        self.batch_scale = 1.0
+        self.what = ("one whole training step on the reference interpreter (oracle/_ref) at full size" if not consts else
+                     "one whole training step on the reference interpreter (oracle/_ref) at reduced size ("
+                     + ", ".join(f"{a} {b}" for a, b in consts.items()) + f"), scaled to the full step by FLOP count x{self.scale:.0f}")
+        outer = self
+
+        class Pause(Exception):
+            pass
+
+        class Stepper(Interpreter):
+            def exec_for(self, st: ir.For):
+                if st.counter.id != hot.counter.id:
+                    return super().exec_for(st)
+                cnt = self.arr(st.counter)
+                cnt[0] = self.bound(st.start)
+                outer.body, outer.counter, outer.step_by = st.body, cnt, st.step
+                raise Pause()
+        self.it = Stepper(c.program, out=open(os.devnull, "w"), seed=0)
+        try:
+            self.it.run()
+        except Pause:
+            pass
+
+    def step(self) -> float:
+        """Seconds of one training step (at the size this object runs)."""
+        t = time.perf_counter()
+        self.it.exec_block(self.body)
+        self.counter[0] += self.step_by
+        return time.perf_counter() - t
+
+
+def cpu_sample(name, batch, budget_s=20.0, steps=1):
+    """The CPU baseline on a bounded sample: whole steps of the reference interpreter itself where oracle/_ref exists
+    (`kind: "reference"`), else of the NumPy port in oracle/kir_interp.py on the first kernels of a step."""
+    try:
+        ref = ReferenceSteps(name)
+    except Exception as e:
+        return cpu_sample_port(name, batch, budget_s, why=str(e))
+    secs = [ref.step() for _ in range(steps)]
+    t = float(np.median(secs))
+    return {"value": batch / (t * ref.scale), "unit": "samples/s", "cores": 1, "kind": "reference", "sample": ref.what,
+            "sample_seconds": t, "scale": ref.scale}
+
+
+def cpu_sample_port(name, batch, budget_s=20.0, why=""):
+    """The oracle (NumPy restatement of the reference interpreter, reduction bodies
     materialised and summed like anvil/interp.py:435-466) runs the program's start-up and then the
     training step's kernels in order until `budget_s` seconds of kernel time have passed. Throughput
     for the whole step is extrapolated by the share of the step's FLOPs that the sample covered."""
@@ -161,28 +241,160 @@ def cpu_sample(name, batch, budget_s=20.0):
     step_seconds = spent * total_flops / max(done_flops, 1)
     return {"value": batch / step_seconds, "unit": "samples/s", "cores": 1, "kind": "port",
             "sample": f"first {n} of {len(kernels)} kernels of one full-size training step "
-                      f"({100.0 * done_flops / total_flops:.2f}% of its FLOPs, {spent:.1f} s), extrapolated by FLOP share"}
+                      f"({100.0 * done_flops / total_flops:.2f}% of its FLOPs, {spent:.1f} s), extrapolated by FLOP share"
+                      + (f" (the reference copy was not usable: {why})" if why else ""),
+            "sample_seconds": spent, "scale": total_flops / max(done_flops, 1)}
 
 
 def reference_arm(args, name, batch, desc):
-    """`--impl reference`: the CPU implementation alone. Each step is one bounded sample."""
+    """`--impl reference`: the CPU implementation alone. Each step is one bounded sample (a whole training step of the
+    reference interpreter, at reduced size where the full size takes hours); `ms_per_step` is the time of a sample,
+    `value` the configuration's throughput that follows from it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    vals, last = [], None
-    for i in range(args.warmup + args.steps):
-        last = cpu_sample(name, batch, budget_s=args.cpu_budget)
-        if i >= args.warmup:
-            vals.append(last["value"])
-    v = float(np.median(vals))
-    last["value"] = v
+    try:
+        ref = ReferenceSteps(name)
+        for _ in range(args.warmup):
+            ref.step()
+        secs = [ref.step() for _ in range(args.steps)]
+        t = float(np.median(secs))
+        last = {"value": batch / (t * ref.scale), "unit": "samples/s", "cores": 1, "kind": "reference", "sample": ref.what,
+                "sample_seconds": t, "scale": ref.scale}
+    except ImportError:
+        vals = []
+        for i in range(args.warmup + args.steps):
+            last = cpu_sample_port(name, batch, budget_s=args.cpu_budget)
+            if i >= args.warmup:
+                vals.append(last["value"])
+        last["value"] = float(np.median(vals))
+        t = last["sample_seconds"]
+    v = last["value"]
     line = {"impl": "reference", "metric": "train samples/s", "value": v, "unit": "samples/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * batch / v, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (program RNG, seed 0)",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (the program's own seeded RNG, seed 0)",
             "config": {"workload": desc, "global_batch": batch}, "cpu_baseline": last,
             "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
     return 0
+
+
+C2_SOURCES = {       # the standalone `anvil.function` kernels of the second BASELINE configuration
+    "rows": ("fn rows(x: [n, d]) = softmax(x)\n", "row softmax f32[4096,4096]"),
+    "ln": ("fn ln(x: [n, d], g: [d], b: [d]) = layer_norm(x) * g + b\n", "layer norm f32[8192,1024]"),
+    "lin": ("fn lin(x: [n, d], W: [d, k], b: [k]):\n    y[i, k] = sum x[i, j] * W[j, k] + b[k]\n    return y\n",
+            "Linear f32[8192,1024] x [1024,4096] + bias"),
+}
+
+
+def c2_inputs(name):
+    rng = np.random.default_rng(0)
+    if name == "rows":
+        return [rng.standard_normal((4096, 4096), dtype=np.float32)]
+    if name == "ln":
+        return [rng.standard_normal((8192, 1024), dtype=np.float32), np.ones(1024, np.float32), np.zeros(1024, np.float32)]
+    return [rng.standard_normal((8192, 1024), dtype=np.float32), rng.standard_normal((1024, 4096), dtype=np.float32) * np.float32(0.02),
+            rng.standard_normal(4096, dtype=np.float32)]
+
+
+def time_training_config(name, batch, steps=20, warmup=3):
+    """(device ms per step, end-to-end ms per step) of a training configuration on one GPU; L2 flushed between steps
+    when a step's traffic would fit in it."""
+    from anvil_lang_b200 import kir
+    from anvil_lang_b200.backend import analysis as an
+    from anvil_lang_b200.feed import HostFeeder, Unsupported, pinned_array
+    from anvil_lang_b200.program import DeviceProgram
+    prog = load_program(name)
+    dp = DeviceProgram(prog, seed=0)
+    try:
+        dp.rtlib.anvil_rt_capture(dp.rt, 1)
+        dp.prologue()
+        hot = an.hot_loop(prog)
+        loss = dp.buffer("loss")
+        step_bytes = sum(an.kernel_bytes(st.kernel) for st in hot.body.stmts if isinstance(st, kir.KernelStmt))
+        flush = step_bytes < 2 * L2_BYTES
+        for _ in range(warmup):
+            dp.step()
+        dp.sync()
+        ms = 0.0
+        for _ in range(steps):
+            if flush:
+                flush_l2(dp)
+            dp.timer_begin()
+            dp.step()
+            ms += dp.timer_end()
+        e2e = None
+        try:
+            feeder = HostFeeder(dp, 0)
+            feeder.load_host_copies()
+            host_loss = pinned_array(dp.rtlib, (1,), np.float32)
+            counter = int(dp.read(hot.counter).reshape(-1)[0])
+            stream = int(dp.rtlib.anvil_rt_get_stream(dp.rt))
+            times = []
+            for i in range(steps + 2):
+                t0 = time.perf_counter()
+                feeder.prepare(counter, stream, dp.seed)
+                feeder.push()
+                dp.step_fed()
+                dp.copy_out_async(host_loss.ctypes.data, loss, 4)
+                dp.sync()
+                times.append(time.perf_counter() - t0)
+                counter += hot.step
+                stream += feeder.rand_streams
+            e2e = 1e3 * float(np.mean(times[2:]))
+        except Unsupported:
+            pass
+        return {"ms_per_step": ms / steps, "samples_per_s": batch * steps / (ms * 1e-3),
+                "e2e_ms_per_step": e2e, "e2e_samples_per_s": (batch / (e2e * 1e-3)) if e2e else None,
+                "l2": "flushed between timed steps" if flush else "step traffic exceeds L2"}
+    finally:
+        dp.close()
+
+
+def time_function_config(name):
+    """A standalone function: device microseconds of a call with the arguments resident in the arena, and milliseconds of
+    the reference-facing call (NumPy arrays in pageable host memory in, NumPy array out)."""
+    from anvil_lang_b200 import pyapi
+    src, what = C2_SOURCES[name]
+    f = pyapi.function(src, name=name)
+    args = c2_inputs(name)
+    out = f(*args)                                       # compiles / loads, first call
+    comp = f.lower(*args)
+    dp = comp.dp
+    for _ in range(3):
+        comp.run_resident()
+    dp.sync()
+    best = 1e9
+    for _ in range(10):
+        flush_l2(dp)
+        dp.timer_begin()
+        comp.run_resident()
+        best = min(best, dp.timer_end())
+    times = []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        out = f(*args)
+        times.append(time.perf_counter() - t0)
+    nbytes_in, nbytes_out = sum(a.nbytes for a in args), out.nbytes
+    return {"what": what, "device_us": 1e3 * best, "e2e_ms": 1e3 * float(np.median(times)),
+            "h2d_bytes": nbytes_in, "d2h_bytes": nbytes_out}
+
+
+def other_configs():
+    """The BASELINE configurations besides the headline one, each device-timed and end to end (one GPU)."""
+    out = {}
+    for key in ("c1", "c3", "c4"):
+        name, batch, desc = WORKLOADS[key]
+        try:
+            out[key] = dict(time_training_config(name, batch), workload=desc)
+        except Exception as e:                           # a secondary measurement must not lose the headline line
+            out[key] = {"error": str(e)[:200]}
+    for name in C2_SOURCES:
+        try:
+            out["c2_" + name] = time_function_config(name)
+        except Exception as e:
+            out["c2_" + name] = {"error": str(e)[:200]}
+    return out
 
 
 def main():
@@ -194,6 +406,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-configs", action="store_true", help="skip the other BASELINE configurations")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     name, batch, desc = WORKLOADS[args.workload]
@@ -214,6 +427,10 @@ def main():
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(device)
+        if rank == 0:                                    # the communicator's own report (ranks, transport) goes to stderr
+            os.environ.setdefault("NCCL_DEBUG", "INFO")
+            os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+            os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{device}"))
         if batch % world:
             raise SystemExit(f"global batch {batch} does not divide over {world} GPUs")
@@ -223,8 +440,10 @@ def main():
 
     dp = DeviceProgram(prog, seed=0, device=device)
     dp.set_rank(rank)
+    comm = None
     if world > 1:
-        dpmod.attach(dp, device)
+        nranks = dpmod.attach_native(dp, rank, world)        # NCCL inside the runtime; the id travelled through the process group
+        comm = {"backend": "nccl in libanvil_cuda.so (ncclAllReduce on the program's stream)", "nranks": nranks}
     dp.rtlib.anvil_rt_capture(dp.rt, 1)                 # the program's own prints stay off stdout
     dp.prologue()
     loss = dp.buffer("loss")
@@ -321,43 +540,53 @@ def main():
     for (kind, idx), unote, ks in dp.gen.hot_units:
         rows.append((dp.time_kernel(idx if kind == "k" else nk + idx, 3), unote, ks))
     total_k = sum(r[0] for r in rows)
-    # Launches of the same generated kernel (same template, shape and statements; only the tensors differ) are
-    # one kernel: the dominant one is the group with the largest total time, and the roofline is that of its
-    # average launch.
-    groups: dict = {}
+    # A kernel = one __global__ template; its launches differ in shape and statements only. Launch units are grouped by
+    # the template they run (the first words of their strategy note); the dominant kernel is the template with the most
+    # time in the step, and its roofline is that of its launches taken together: their algorithmic FLOPs (or bytes)
+    # over their summed CUDA-event time.
+    def template_of(unote):
+        w = unote.split()
+        return " ".join(w[:2]) if w[0] in ("gemm", "attention", "split", "coop", "eltwise", "rowgroup") else w[0]
+    by_template: dict = {}
     for t, unote, ks in rows:
-        key = (" ".join(unote.split()[:3]) if unote.startswith("gemm") else unote, "+".join(k_.label for k_ in ks))
-        g = groups.setdefault(key, [0.0, 0, ks, unote])
-        g[0] += t
-        g[1] += 1
-    (_, _), (grp_ms, grp_n, top_ks, note) = max(groups.items(), key=lambda kv: kv[1][0])
-    top_ms = grp_ms / grp_n
-    top = top_ks[0]
+        by_template.setdefault(template_of(unote), []).append((t, unote, ks))
+    top_name, top_rows = max(by_template.items(), key=lambda kv: sum(r[0] for r in kv[1]))
+    top_ms = sum(r[0] for r in top_rows)
     peaks = measured_peaks()
-    common = {"kernel": f"{top.name} {top.label} [{note}]", "launches_per_step": grp_n, "avg_launch_ms": top_ms,
-              "share_of_step": grp_ms / total_k}
-    if note.startswith("gemm"):
-        tf32 = measure_tf32_peak()
-        flops = an.kernel_flops(top)
+    tf32 = measure_tf32_peak()
+    tensor_peak = (tf32 / 3.0) if tf32 else 1590.0 / 2 / 3
+    tensor_src = ("torch.matmul tf32 8192^3 best of 10 (cuBLAS), measured in this run: %.0f TFLOP/s, / 3 for 3xTF32; the tensor "
+                  "pipe's own issue ceiling for kind::tf32, measured with a stand-alone issue loop, is 991 TFLOP/s" % tf32) if tf32 \
+        else "fallback: half the bf16 fallback peak / 3"
+    unit_flops = lambda ks: sum(an.kernel_flops(k_) for k_ in ks)
+    common = {"kernel": f"{top_name} (all {len(top_rows)} launches of the template in one step)", "launches_per_step": len(top_rows),
+              "avg_launch_ms": top_ms / len(top_rows), "share_of_step": top_ms / total_k}
+    shapes: dict = {}
+    for t, unote, ks in top_rows:
+        g = shapes.setdefault(" ".join(unote.split()[:3]) + " <" + "+".join(sorted({k_.label for k_ in ks}))[:40] + ">", [0.0, 0, 0.0, 0.0])
+        g[0] += t; g[1] += 1; g[2] += unit_flops(ks); g[3] += an.group_bytes(ks, dp.gen.dead_roots)
+    if top_name.startswith("gemm"):
+        flops = sum(unit_flops(ks) for _, _, ks in top_rows)
         achieved = flops / (top_ms * 1e-3) / 1e12
-        peak = (tf32 / 3.0) if tf32 else 1590.0 / 2 / 3
-        gemm_ms = sum(t for t, unote, _ in rows if unote.startswith("gemm"))
-        gemm_flops = sum(an.kernel_flops(ks[0]) for _, unote, ks in rows if unote.startswith("gemm"))
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": next((v for k_, v in NCU_TRAFFIC.items() if note.startswith(k_)), None), **common,
-                "all_contractions": {"share_of_step": gemm_ms / total_k, "achieved": gemm_flops / (gemm_ms * 1e-3) / 1e12},
-                "peak_source": "torch.matmul tf32 8192^3 best of 10, measured in this run, / 3 for 3xTF32" if tf32
-                else "fallback: half the bf16 fallback peak / 3"}
+        roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s", "frac": achieved / tensor_peak,
+                "traffic": NCU_TRAFFIC_PER_LAUNCH.get(top_name), **common, "peak_source": tensor_src,
+                "by_shape": {k_: {"ms": round(v[0], 3), "launches": v[1], "TFLOP/s": round(v[2] / (v[0] * 1e-3) / 1e12, 1)}
+                             for k_, v in sorted(shapes.items(), key=lambda kv: -kv[1][0])[:10]}}
     else:
-        nbytes = an.group_bytes(top_ks, dp.gen.dead_roots)
+        nbytes = sum(an.group_bytes(ks, dp.gen.dead_roots) for _, _, ks in top_rows)
         achieved = nbytes / (top_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, **common, "peak_source": peaks["source"]}
+                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_PER_LAUNCH.get(top_name), **common,
+                "peak_source": peaks["source"]}
     classes = {}
     for t, unote, _ in rows:
-        c = " ".join(unote.split()[:2])
+        c = template_of(unote)
         classes[c] = classes.get(c, 0.0) + t
     roof["step_ms_by_class"] = {c: round(v, 3) for c, v in sorted(classes.items(), key=lambda kv: -kv[1])}
+    step_flops_all = sum(an.kernel_flops(k_) for k_ in kernels)
+    roof["whole_step"] = {"flops": step_flops_all, "achieved": step_flops_all / (ms / K * 1e-3) / 1e12, "unit": "TFLOP/s",
+                          "frac": step_flops_all / (ms / K * 1e-3) / 1e12 / tensor_peak,
+                          "note": "all FLOPs of a step (contractions are 94 % of them) over the step time, against the 3xTF32 roof"}
 
     cpu = None if (args.no_cpu or world > 1) else cpu_sample(name, batch, budget_s=args.cpu_budget)
     line = {"metric": "train samples/s", "value": value, "unit": "samples/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -368,6 +597,11 @@ def main():
                        else "L2 flushed with a 256 MB write between timed steps"},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clk, "roofline": roof, "cpu_baseline": cpu,
             "wall_ms_per_step": 1e3 * wall / K, "last_loss": last_loss}
+    if comm is not None:
+        line["comm"] = comm
+    if world == 1 and not args.no_configs and args.workload == "c5":
+        dp.close()
+        line["configs"] = other_configs()
     print(json.dumps(line))
     if dist is not None:
         dist.barrier()

@@ -54,6 +54,12 @@ int anvil_rt_d2h(anvil_rt *rt, void *dst, size_t off, size_t bytes);         /* 
 int anvil_rt_d2d_async(anvil_rt *rt, size_t off, const void *src_device, size_t bytes, void *producer_stream);
 int anvil_rt_h2d_async(anvil_rt *rt, size_t off, const void *pinned_src, size_t bytes);
 int anvil_rt_d2h_async(anvil_rt *rt, void *pinned_dst, size_t off, size_t bytes);
+/* Large copies from / to PAGEABLE host memory — the caller's own arrays behind the `anvil_input{k}` / `anvil_output{k}`
+ * slots of anvil/pyapi.py:282-299: cut into 8 MiB chunks that go through two pinned buffers of the context, host threads
+ * filling (draining) one while the DMA engine moves the other. h2d_staged is stream-ordered and has consumed `src` when
+ * it returns; d2h_staged returns with the data in `dst`. Small copies fall through to the plain calls. */
+int anvil_rt_h2d_staged(anvil_rt *rt, size_t off, const void *src, size_t bytes);
+int anvil_rt_d2h_staged(anvil_rt *rt, void *dst, size_t off, size_t bytes);
 int anvil_rt_zero(anvil_rt *rt, size_t off, size_t bytes);
 int anvil_rt_sync(anvil_rt *rt);                              /* anvil_sync, anvil_cuda.h:55-58    */
 void *anvil_rt_host_alloc(size_t bytes);                      /* pinned host memory                */
@@ -179,10 +185,19 @@ int anvil_rt_tensor_map(anvil_rt *rt, void *map_out, size_t off, long rows, long
 
 /* ---- the data-parallel collective (no reference counterpart: the reference is single-device).
  * Sums `count` f32 values at arena offset `off` over all ranks, in place, stream-ordered. The
- * collective itself is supplied by the host program (NCCL through torch.distributed in this repo). */
+ * collective is either supplied by the host program through the callback below, or the runtime's own (next block). */
 typedef int (*anvil_allreduce_fn)(void *user, void *device_ptr, long count, void *cuda_stream);
 void anvil_rt_set_allreduce(anvil_rt *rt, anvil_allreduce_fn fn, void *user);
 int anvil_rt_allreduce(anvil_rt *rt, size_t off, long count);
+/* The collective inside the runtime: NCCL (dlopen'ed "libnccl.so.2") over NVLink / NVSwitch, so that a C host can run
+ * data parallel without Python. Rank 0 makes a 128-byte id and hands it to the other ranks by whatever means the host
+ * program has; every rank then joins. After anvil_rt_comm_init, anvil_rt_allreduce is ncclAllReduce(sum, f32) in place on
+ * the arena, ordered on the context's stream. Algorithm, protocol and channel count are pinned (Ring / Simple / 8) unless
+ * the environment sets them, for run-to-run identical sums at a given number of ranks. */
+int anvil_rt_comm_unique_id(void *id_out, size_t bytes);
+int anvil_rt_comm_init(anvil_rt *rt, int rank, int nranks, const void *unique_id, size_t bytes);
+int anvil_rt_comm_nranks(anvil_rt *rt);            /* ranks of the communicator this context joined, 0 if none */
+int anvil_rt_comm_destroy(anvil_rt *rt);
 
 /* ---- the bounded wait of the tensor-core templates, exercised on purpose (no reference counterpart: the
  * reference's kernels never wait on one another). Runs one tiny kernel that waits, with a limit of `limit_clocks`

@@ -10,7 +10,9 @@ torch.cuda.set_device(dev)
 dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{dev}"))
 path, steps = sys.argv[1], int(sys.argv[2])
 prog = dpmod.shard(kir.load(path), world)
-p = DeviceProgram(prog, device=dev); p.set_rank(rank); dpmod.attach(p, dev)
+p = DeviceProgram(prog, device=dev); p.set_rank(rank)
+if os.environ.get("ANVIL_DP_COLLECTIVE", "native") == "native": dpmod.attach_native(p, rank, world)
+else: dpmod.attach(p, dev)
 p.rtlib.anvil_rt_capture(p.rt, 1)
 p.prologue(); loss = p.buffer("loss"); out = []
 for i in range(steps):
