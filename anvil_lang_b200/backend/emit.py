@@ -468,7 +468,8 @@ class KernelGen:
                 S = 1
                 per_thread = RN // RY
                 if groups < 148 and per_thread >= 64:
-                    S = max(1, min(296 // groups, per_thread // 32, 64))
+                    # enough CTAs for four per SM, each thread still adding eight rows or more
+                    S = max(1, min(592 // groups, per_thread // 8, 128))
                 return ("coop4", OX, RY, S)
         blocks = (ON + OX - 1) // OX
         S = 1
@@ -732,7 +733,7 @@ class KernelGen:
         lines += self.decode("u", k.domain, self.names, ind, vv, 4) + self.lane_vars(vv, 4, ind)
         lines.append(f"{ind}float acc_0 = {OP}::id<float>(), acc_1 = acc_0, acc_2 = acc_0, acc_3 = acc_0;")
         lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RN}L, rbeg + {chunk}L);")
-        lines.append("#pragma unroll 4")                 # several rows' loads in flight; the adds keep their order
+        lines.append("#pragma unroll 8")                 # several rows' loads in flight; the adds keep their order
         lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
         inner = ind + "    "
         lines.append(f"{inner}const {index_t(RN)} rr = ({index_t(RN)})rr_;")
@@ -780,20 +781,29 @@ class KernelGen:
                 self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
         saved = self.ptrs
         self.ptrs = {}
-        fsc = Scope(self, self.names, 1, None, "        ")
+        fsc = Scope(self, self.names, 1, None, "            ")
         fsc.statements()
-        fl = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {ON}L; tid += (long)gridDim.x * {THREADS}L) {{",
+        # 64 outputs x 4 slices per CTA: slice q adds partials q, q + 4, ... in order, the four slice sums are combined
+        # as (s0 + s1) + (s2 + s3): a fixed tree, and four times as many loads in flight as one thread per output
+        FO, FS = 64, 4
+        fl = [f"    const int fo = threadIdx.x % {FO}, fq = threadIdx.x / {FO};",
+              f"    const long tid = blockIdx.x * {FO}L + fo;",
+              f"    const bool live = tid < {ON}L;",
+              f"    float part = {OP}::id<float>();",
+              "#pragma unroll 8",
+              f"    for (int p = fq; p < {S}; p += {FS}) if (live) part = {OP}::f(part, ((const float *)(A + {soff}UL))[p * {ON}L + tid]);",
+              f"    __shared__ float fin_[{FS}][{FO}];",
+              "    fin_[fq][fo] = part;",
+              "    __syncthreads();",
+              "    if (fq == 0 && live) {",
+              f"        const float acc = {OP}::f({OP}::f(fin_[0][fo], fin_[1][fo]), {OP}::f(fin_[2][fo], fin_[3][fo]));",
               f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
         fl += self.decode("u", k.domain, self.names, "        ")
-        fl.append(f"        float acc = {OP}::id<float>();")
-        fl.append("#pragma unroll 8")
-        fl.append(f"        for (int p = 0; p < {S}; p++) acc = {OP}::f(acc, ((const float *)(A + {soff}UL))[p * {ON}L + tid]);")
         final = [self.comment("split reduction, part 2 of 2"), self.head(base, THREADS)] + self.pointer_decls() \
             + fl + fsc.lines + ["    }", "}"]
         self.ptrs = {**saved, **self.ptrs}
         launch.append(self.launch_line(base + "_part", f"dim3({gx}, {S})", nthreads))
-        fb = max(1, min((ON + THREADS - 1) // THREADS, MAX_BLOCKS))
-        launch.append(self.launch_line(base, fb, THREADS))
+        launch.append(self.launch_line(base, (ON + FO - 1) // FO, THREADS))
         self.notes = f"split col4 {OX}x{RY} S{S}"
         return "\n".join(part) + "\n\n" + "\n".join(final), launch
 
