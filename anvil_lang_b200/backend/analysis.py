@@ -306,7 +306,7 @@ def _lifetime(us, loops):
     return lo, hi
 
 
-def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256, share: bool = True, fused_runs=None,
+def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256 + 4 * 256, share: bool = True, fused_runs=None,
                keep=()) -> ArenaPlan:
     """One arena for the whole program. Temporaries (`temp`, `grad`) whose first use writes all of them and whose
     lifetimes do not overlap share bytes (first fit by decreasing size, ids break ties: the layout is the same every

@@ -771,41 +771,57 @@ class KernelGen:
             launch.append(self.launch_line(base, f"dim3({gx}, 1)", nthreads))
             self.notes = f"coop col4 {OX}x{RY}"
             return "\n".join(src), launch
+        # Split over S CTAs per output group, finished by whichever of them arrives last: every CTA writes its partial
+        # sums to scratch and takes a ticket; the last one adds all S partials in a fixed order (slice ry takes partials
+        # ry, ry + RY, ..., then the same shared-memory tree) and runs the statements. The result does not depend on which
+        # CTA is last, and there is no second launch.
         self.gen.need_scratch(4 * ON * S)
         soff = self.gen.plan.scratch_off
+        assert gx <= 256, "ticket counters"
+        tree = []
+        for i in range(4):
+            tree.append(f"{ind}sm_[ry][4 * ox + {i}] = acc_{i};")
+        tree.append(f"{ind}__syncthreads();")
+        s_ = RY // 2
+        while s_ >= 1:
+            tree.append(f"{ind}if (ry < {s_}) {{ " + " ".join(
+                f"sm_[ry][4 * ox + {i}] = {OP}::f(sm_[ry][4 * ox + {i}], sm_[ry + {s_}][4 * ox + {i}]);" for i in range(4)) + " }")
+            tree.append(f"{ind}__syncthreads();")
+            s_ //= 2
+        for i in range(4):
+            tree.append(f"{ind}acc_{i} = sm_[0][4 * ox + {i}];")
+        lines.append(f"{ind}float *part_ = (float *)(A + {soff}UL);")
         lines.append(f"{ind}if (ry == 0 && live) {{")
         for i in range(4):
-            lines.append(f"{ind}    ((float *)(A + {soff}UL))[blockIdx.y * {ON}L + o_ * 4 + {i}] = acc_{i};")
+            lines.append(f"{ind}    part_[blockIdx.y * {ON}L + o_ * 4 + {i}] = acc_{i};")
         lines.append(f"{ind}}}")
-        part = [self.comment(f"split reduction, part 1 of 2 (col, 4 outputs per thread, {S} CTAs per output group)"),
-                self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
-        saved = self.ptrs
-        self.ptrs = {}
-        fsc = Scope(self, self.names, 1, None, "            ")
-        fsc.statements()
-        # 64 outputs x 4 slices per CTA: slice q adds partials q, q + 4, ... in order, the four slice sums are combined
-        # as (s0 + s1) + (s2 + s3): a fixed tree, and four times as many loads in flight as one thread per output
-        FO, FS = 64, 4
-        fl = [f"    const int fo = threadIdx.x % {FO}, fq = threadIdx.x / {FO};",
-              f"    const long tid = blockIdx.x * {FO}L + fo;",
-              f"    const bool live = tid < {ON}L;",
-              f"    float part = {OP}::id<float>();",
-              "#pragma unroll 8",
-              f"    for (int p = fq; p < {S}; p += {FS}) if (live) part = {OP}::f(part, ((const float *)(A + {soff}UL))[p * {ON}L + tid]);",
-              f"    __shared__ float fin_[{FS}][{FO}];",
-              "    fin_[fq][fo] = part;",
-              "    __syncthreads();",
-              "    if (fq == 0 && live) {",
-              f"        const float acc = {OP}::f({OP}::f(fin_[0][fo], fin_[1][fo]), {OP}::f(fin_[2][fo], fin_[3][fo]));",
-              f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
-        fl += self.decode("u", k.domain, self.names, "        ")
-        final = [self.comment("split reduction, part 2 of 2"), self.head(base, THREADS)] + self.pointer_decls() \
-            + fl + fsc.lines + ["    }", "}"]
-        self.ptrs = {**saved, **self.ptrs}
-        launch.append(self.launch_line(base + "_part", f"dim3({gx}, {S})", nthreads))
-        launch.append(self.launch_line(base, (ON + FO - 1) // FO, THREADS))
+        lines += [f"{ind}__threadfence();", f"{ind}__shared__ unsigned last_;", f"{ind}__syncthreads();",
+                  f"{ind}unsigned *ticket_ = (unsigned *)(A + ANVIL_RT_TICKETS_OFF) + blockIdx.x;",
+                  f"{ind}if (threadIdx.x == 0) last_ = atomicAdd(ticket_, 1u) == {S - 1}u;",
+                  f"{ind}__syncthreads();", f"{ind}if (!last_) return;", f"{ind}__threadfence();"]
+        for i in range(4):
+            lines.append(f"{ind}acc_{i} = {OP}::id<float>();")
+        lines.append(f"{ind}if (live) {{")
+        lines.append("#pragma unroll 4")
+        lines.append(f"{ind}    for (int p = ry; p < {S}; p += {RY}) {{")
+        for i in range(4):
+            lines.append(f"{ind}        acc_{i} = {OP}::f(acc_{i}, __ldcg(part_ + p * {ON}L + o_ * 4 + {i}));")
+        lines.append(f"{ind}    }}")
+        lines.append(f"{ind}}}")
+        lines.append(f"{ind}__syncthreads();")
+        lines += tree
+        lines.append(f"{ind}if (threadIdx.x == 0) *ticket_ = 0u;")
+        tail = Scope(self, self.names, 4, vv, ind + "    ")
+        tail.acc_lanes = True
+        tail.statements()
+        lines.append(f"{ind}if (ry == 0 && live) {{")
+        lines += tail.lines
+        lines.append(f"{ind}}}")
+        src = [self.comment(f"split reduction finished by the last CTA (col, 4 outputs per thread, {S} CTAs per output group)"),
+               self.head(base, nthreads)] + self.pointer_decls() + lines + ["}"]
+        launch.append(self.launch_line(base, f"dim3({gx}, {S})", nthreads))
         self.notes = f"split col4 {OX}x{RY} S{S}"
-        return "\n".join(part) + "\n\n" + "\n".join(final), launch
+        return "\n".join(src), launch
 
     # ---- contractions
     def functor_method(self, sig: str, decodes: list, build) -> list[str]:

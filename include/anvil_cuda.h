@@ -30,6 +30,9 @@ extern "C" {
 #define ANVIL_RT_STREAM_OFF 16      /* uint32: device copy of the random stream counter           */
 #define ANVIL_RT_STATUS_OFF 32      /* uint32: status word written by kernels that give up a wait */
 #define ANVIL_RT_CHECK_OFF 48       /* uint64: smallest bad index found by the last --check scan     */
+#define ANVIL_RT_TICKETS_OFF 256    /* 256 x uint32 after the header: arrival counters of split reductions that finish in
+                                       their last CTA; zero between launches                                       */
+#define ANVIL_RT_TICKETS 256
 
 typedef struct anvil_rt anvil_rt;
 
