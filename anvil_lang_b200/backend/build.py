@@ -76,8 +76,7 @@ def build_runtime(force: bool = False) -> str:
 def program_flags():
     # -fmad=false: f32 arithmetic is done operation by operation, like the NumPy interpreter that
     # defines the results; IEEE division and square root are nvcc's defaults without fast-math.
-    extra = [f"-DANVIL_TC_RAW_HI={os.environ['ANVIL_TC_RAW_HI']}"] if os.environ.get("ANVIL_TC_RAW_HI") else []
-    return ["-O3", "-std=c++17", "-lineinfo", "-fmad=false", "-w", *ARCH_FLAGS, "-I", INCLUDE, "-I", CSRC, *extra]
+    return ["-O3", "-std=c++17", "-lineinfo", "-fmad=false", "-w", *ARCH_FLAGS, "-I", INCLUDE, "-I", CSRC]
 
 
 def build_program(source: str, path: str | None = None) -> str:
@@ -86,7 +85,7 @@ def build_program(source: str, path: str | None = None) -> str:
     deps = _stamp([os.path.join(CSRC, "anvil_device.cuh"), os.path.join(CSRC, "anvil_rng.h"),
                    os.path.join(CSRC, "anvil_gemm_simt.cuh"), os.path.join(CSRC, "anvil_gemm_sm100.cuh"),
                    os.path.join(CSRC, "anvil_attn_sm100.cuh"), os.path.join(INCLUDE, "anvil_cuda.h")])
-    key = hashlib.sha256((source + deps + os.environ.get("ANVIL_TC_RAW_HI", "")).encode()).hexdigest()[:16]
+    key = hashlib.sha256((source + deps).encode()).hexdigest()[:16]
     lib = path or os.path.join(BUILD_DIR, f"prog-{key}.so")
     if os.path.exists(lib) and path is None:
         return lib

@@ -7,12 +7,15 @@
 //
 //   product 1   S[128 x T]  = A1[128 x DH] * B1[T x DH]^T       tcgen05.mma kind::tf32, 3xTF32, accumulator in TMEM
 //   row phase   two warps per TMEM lane quarter, alternate 32-column chunks each; thread = row
-//       forward   s = post(alpha1 * S, i, j);  m = max_j s;  e = exp(s - m);  sum = sum_j e;  p = e / sum
+//       forward   s = post(alpha1 * S, i, j);  m = max_j s;  e = exp(s - m);  sum = sum_j e;  p = e * (1 / sum)
 //       backward  dp = S;  dt = sum_j dp * (-p / sum);  ds = (dp * (1 / sum) + dt) * e        (p, e, sum: from memory)
-//     the row's result (p, or ds) goes to memory when a later kernel reads it, and — split into hi/lo — straight
-//     back into TMEM as the A operand of
-//   product 2   O[128 x DH] = R[128 x T] * B2[T x DH]          (A from tensor memory, B2 from shared memory)
-//   epilogue    the second product's own statements on O (transposed through shared memory, coalesced).
+//     e, p and ds go to memory when a later kernel reads them; R = e (forward) or ds (backward) goes — split into
+//     hi/lo, chunk by chunk as the last pass over the row produces it — straight back into TMEM as the A operand of
+//   product 2   O[128 x DH] = R[128 x T] * B2[T x DH]          (A from tensor memory, B2 from shared memory; even and odd
+//                                                               chunks of T into two accumulators, so two chains run)
+//   epilogue    O = (even + odd) * scale, scale = 1 / sum of the row in the forward direction (product 2 ran on e, not
+//               on p: it does not have to wait for the row sums), then the second product's own statements on O
+//               (transposed through shared memory, coalesced).
 //
 // With a causal mask, query rows 0..127 cannot see keys 128..T-1: their CTA runs both products over 128 keys only
 // and writes exact zeros for the rest (what exp(-1e9 - m) is in f32).
@@ -29,7 +32,8 @@ namespace attn {
 using namespace anvil::tc;
 
 constexpr int QROWS = 128, ROW_WARPS = 8, CONV_WARPS = 8, MMA_W = ROW_WARPS + CONV_WARPS, THREADS_ATT = 32 * (MMA_W + 1);
-constexpr uint32_t COL_S = 0, COL_O = 256, COL_R = 320;            // TMEM columns: S (256), O (64), two R stages of 64 (hi 32 | lo 32)
+constexpr int STAGE_FLOATS = 16 * 36;                                 // per row warp: 16 rows of 32 floats, rows 144 bytes apart
+constexpr uint32_t COL_S = 0, COL_O = 256, COL_R = 384;            // TMEM columns: S (256), two O accumulators of 64, two R stages of 64 (hi 32 | lo 32)
 
 __host__ __device__ constexpr uint32_t region_bytes(int t, int dh) {
     // phase 1: A1 and B1 for all of DH (hi + lo); phase 2 (overlaid): B2 for all of T (hi + lo)
@@ -37,7 +41,7 @@ __host__ __device__ constexpr uint32_t region_bytes(int t, int dh) {
     const uint32_t p2 = (uint32_t)(t / BK) * 2u * tile_bytes(dh);
     return p1 > p2 ? p1 : p2;
 }
-__host__ __device__ constexpr uint32_t smem_bytes_att(int t, int dh) { return region_bytes(t, dh) + 4 * 32 * 33 * 4 + 1024 + 256; }
+__host__ __device__ constexpr uint32_t smem_bytes_att(int t, int dh) { return region_bytes(t, dh) + ROW_WARPS * STAGE_FLOATS * 4 + 1024 + 256; }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -55,6 +59,59 @@ __device__ __forceinline__ void tmem_st16_at(uint32_t taddr, const uint32_t *r) 
 }
 __device__ __forceinline__ void row_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }      // the eight row warps only
 
+// A thread owns a row (the TMEM lane), but 32 lanes each moving 16 bytes of a different row cost the load/store unit 32
+// lines per instruction. Chunks of W columns therefore pass through shared memory, 16 rows at a time: towards memory the
+// owners write their rows, then W / 4 lanes move one row's 4 W bytes; from memory the other way round.
+// stage = the warp's 16 x 36 floats, base = the chunk's first element in the warp's first row, rs = floats between rows.
+template <int W>
+__device__ __forceinline__ void tile_store(float *stage, int lane, float *base, int rs, const uint32_t *r) {
+    constexpr int LPR = W / 4, RPI = 32 / LPR;
+    const int srow = lane / LPR, scol = 4 * (lane % LPR);
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        if ((lane >> 4) == half) {
+#pragma unroll
+            for (int x = 0; x < W; x += 4)
+                *reinterpret_cast<float4 *>(stage + (lane & 15) * 36 + x) = make_float4(__uint_as_float(r[x]), __uint_as_float(r[x + 1]),
+                                                                                        __uint_as_float(r[x + 2]), __uint_as_float(r[x + 3]));
+        }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 16 / RPI; k++)
+            *reinterpret_cast<float4 *>(base + (16 * half + RPI * k + srow) * rs + scol) =
+                *reinterpret_cast<const float4 *>(stage + (RPI * k + srow) * 36 + scol);
+        __syncwarp();
+    }
+}
+// From memory, 16 columns at a time, in two steps so that the loads of the next tile fly while this one is worked on:
+// fetch (four 16-byte loads per lane: 4 lanes per row, 8 rows per instruction) and, later, the hand-over to the owners.
+__device__ __forceinline__ void tile_fetch16(int lane, const float *base, int rs, float4 (&raw)[4]) {
+    const int srow = lane >> 2, scol = 4 * (lane & 3);
+#pragma unroll
+    for (int k = 0; k < 4; k++) raw[k] = *reinterpret_cast<const float4 *>(base + (8 * k + srow) * rs + scol);
+}
+__device__ __forceinline__ void tile_hand_over16(float *stage, int lane, const float4 (&raw)[4], float *v) {
+    const int srow = lane >> 2, scol = 4 * (lane & 3);
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+#pragma unroll
+        for (int k = 0; k < 2; k++) *reinterpret_cast<float4 *>(stage + (8 * k + srow) * 36 + scol) = raw[2 * half + k];
+        __syncwarp();
+        if ((lane >> 4) == half) {
+#pragma unroll
+            for (int x = 0; x < 16; x += 4) {
+                const float4 t4 = *reinterpret_cast<const float4 *>(stage + (lane & 15) * 36 + x);
+                v[x] = t4.x; v[x + 1] = t4.y; v[x + 2] = t4.z; v[x + 3] = t4.w;
+            }
+        }
+        __syncwarp();
+    }
+}
+__device__ __forceinline__ void tile_zero32(int lane, float *base, int rs) {
+#pragma unroll
+    for (int k = 0; k < 8; k++) *reinterpret_cast<float4 *>(base + (4 * k + (lane >> 3)) * rs + 4 * (lane & 7)) = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 // F (generated):
 //   T, DH, NBH, MODE (0 forward, 1 backward), CAUSAL, ALPHA1, ALPHA2, STORE_R, STORE_E, STORE_SUM, STORE_MAX
 //   a1(i, k, bh, v[4]), b1(k, j, bh, v[4])      operands of product 1 (4 consecutive k)
@@ -70,7 +127,7 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
     static_assert(T == 256 && DH == 64, "the template is laid out for T = 256, DH = 64");
     constexpr uint32_t TA1 = tile_bytes(QROWS), TB1 = tile_bytes(T), TB2 = tile_bytes(DH);
     constexpr uint32_t LBO_A1 = lbo_bytes(QROWS), LBO_B1 = lbo_bytes(T), LBO_B2 = lbo_bytes(DH);
-    constexpr uint32_t REGION = region_bytes(T, DH), EPI_OFF = REGION, RED_OFF = EPI_OFF + 4 * 32 * 33 * 4, BAR_OFF = RED_OFF + 1024;
+    constexpr uint32_t REGION = region_bytes(T, DH), EPI_OFF = REGION, RED_OFF = EPI_OFF + ROW_WARPS * STAGE_FLOATS * 4, BAR_OFF = RED_OFF + 1024;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int WORK = F::NBH * NQT;
 
@@ -100,7 +157,11 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
 
-    // item w -> (batch x head, query tile); keys this tile can see
+    // item w of a CTA's n-th round -> (batch x head, query tile); keys this tile can see. With a causal mask the later
+    // query tile is about twice the work of the earlier one, and w % NQT alone would give a CTA the same tile every
+    // round (the grid is a multiple of NQT wide): the tile index rotates with the round, so every CTA gets both kinds.
+    const bool rotate = gridDim.x % NQT == 0;
+    auto tile_of = [&](int w, int n) { return rotate ? (w % NQT + n) % NQT : w % NQT; };
     auto keys_of = [&](int qt) { return F::CAUSAL ? QROWS * (qt + 1) : T; };
 
     if (warp >= ROW_WARPS && warp < MMA_W) {
@@ -108,7 +169,7 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
         const int tc = t - 32 * ROW_WARPS;                                   // 0 .. 255
         int n = 0;
         for (int w = blockIdx.x; w < WORK && !*failed; w += gridDim.x, n++) {
-            const int bh = w / NQT, qt = w % NQT, i0 = qt * QROWS, NK = keys_of(qt);
+            const int bh = w / NQT, qt = tile_of(w, n), i0 = qt * QROWS, NK = keys_of(qt);
             if (!mbar_wait(r_free, (uint32_t)(n & 1) ^ 1u)) { *failed = 1; break; }
             for (int kb = 0; kb < NKB1; kb++) {                                 // all loads of a block first, then the stores: the loads overlap
                 uint8_t *a_hi = smem + kb * 2 * (TA1 + TB1), *a_lo = a_hi + TA1, *b_hi = a_lo + TA1, *b_lo = b_hi + TB1;
@@ -144,7 +205,7 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
                 }
             }
             if (w + (int)gridDim.x < WORK) {                                    // ask L2 for the next item's operands: one 128-byte line per call
-                const int w2 = w + gridDim.x, bh2 = w2 / NQT, qt2 = w2 % NQT, NK2 = keys_of(qt2);
+                const int w2 = w + gridDim.x, bh2 = w2 / NQT, qt2 = tile_of(w2, n + 1), NK2 = keys_of(qt2);
                 if (tc < QROWS * (DH / 32)) f.a1_touch(qt2 * QROWS + tc / (DH / 32), 32 * (tc % (DH / 32)), bh2);
                 for (int x = tc; x < NK2 * (DH / 32); x += 256) f.b1_touch(32 * (x % (DH / 32)), x / (DH / 32), bh2);
                 for (int x = tc; x < NK2 * (DH / 32); x += 256) f.b2_touch(x / (DH / 32), 32 * (x % (DH / 32)), bh2);
@@ -160,7 +221,7 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
             uint32_t pcount[2] = {0u, 0u};
             int n = 0;
             for (int w = blockIdx.x; w < WORK && !*failed; w += gridDim.x, n++) {
-                const int qt = w % NQT, NK = keys_of(qt);
+                const int qt = tile_of(w, n), NK = keys_of(qt);
                 const uint32_t idesc1 = instr_desc(QROWS, NK), idesc2 = instr_desc(QROWS, DH);
                 if (!mbar_wait(qk_full, (uint32_t)(n & 1))) { *failed = 1; break; }
                 if (!mbar_wait(s_free, (uint32_t)(n & 1) ^ 1u)) { *failed = 1; break; }
@@ -187,12 +248,13 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t b_hi = base + kb * 2 * TB2, b_lo = b_hi + TB2;
                     const uint32_t a_hi = tmem + COL_R + 64u * s, a_lo = a_hi + 32u;
+                    const uint32_t acc = tmem + COL_O + 64u * s;                     // even and odd chunks: accumulators of their own, two chains in flight
 #pragma unroll
                     for (int j = 0; j < BK / 8; j++) {
                         const uint64_t dbh = smem_desc(b_hi + 2 * j * LBO_B2, LBO_B2), dbl = smem_desc(b_lo + 2 * j * LBO_B2, LBO_B2);
-                        mma_tf32_ts(tmem + COL_O, a_hi + 8u * j, dbl, idesc2, (kb | j) ? 1u : 0u);
-                        mma_tf32_ts(tmem + COL_O, a_lo + 8u * j, dbh, idesc2, 1u);
-                        mma_tf32_ts(tmem + COL_O, a_hi + 8u * j, dbh, idesc2, 1u);
+                        mma_tf32_ts(acc, a_hi + 8u * j, dbl, idesc2, ((kb >> 1) | j) ? 1u : 0u);
+                        mma_tf32_ts(acc, a_lo + 8u * j, dbh, idesc2, 1u);
+                        mma_tf32_ts(acc, a_hi + 8u * j, dbh, idesc2, 1u);
                     }
                     mma_commit(p_free(s));
                 }
@@ -207,62 +269,77 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
         // 128-byte lines of its row and stage h of the A operand belongs to the warps with that h alone
         const int q = warp & 3, h = warp >> 2, row = 32 * q + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(32 * q) << 16);
-        float *stage_f = reinterpret_cast<float *>(smem + EPI_OFF) + q * (32 * 33);        // used by the warp with h == 0 only
+        float *stage_f = reinterpret_cast<float *>(smem + EPI_OFF) + warp * STAGE_FLOATS;  // 16 rows of a 32-column chunk at a time
         uint32_t fcount = 0u;
+        int n = 0;                                                                 // rounds of this CTA
         // The row warps meet at a named barrier, so they must all leave the loop at the same place: a wait that ran out
         // is recorded in a flag of their own and looked at by everybody right after the next barrier.
         volatile uint32_t *rfail = reinterpret_cast<volatile uint32_t *>(smem + BAR_OFF + 144);
         if (t == 0) *rfail = 0;
         row_bar();
-        auto store32 = [](float *dst, const uint32_t (&r)[32]) {
-#pragma unroll
-            for (int x = 0; x < 32; x += 4)
-                *reinterpret_cast<float4 *>(dst + x) = make_float4(__uint_as_float(r[x]), __uint_as_float(r[x + 1]),
-                                                                    __uint_as_float(r[x + 2]), __uint_as_float(r[x + 3]));
+        // one chunk of the second product's A operand: wait for stage h, split 16 columns at a time into hi / lo in tensor
+        // memory, then tell the MMA warp
+        auto feed_begin = [&]() -> bool {
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait(p_free(h), (fcount & 1u) ^ 1u))) return false;      // the warp stays together
+            fcount++;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            return true;
         };
-        int n = 0;
+        auto feed_half = [&](int half, const uint32_t *r16) {
+            uint32_t part[16];
+#pragma unroll
+            for (int x = 0; x < 16; x++) part[x] = r16[x] & 0xFFFFE000u;
+            tmem_st16_at(lane_addr + COL_R + 64u * h + 16u * half, part);
+#pragma unroll
+            for (int x = 0; x < 16; x++) part[x] = __float_as_uint(__uint_as_float(r16[x]) - __uint_as_float(part[x]));
+            tmem_st16_at(lane_addr + COL_R + 64u * h + 32u + 16u * half, part);
+        };
+        auto feed_end = [&]() {
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(h));
+        };
         for (int w = blockIdx.x; w < WORK; w += gridDim.x, n++) {
-            const int bh = w / NQT, qt = w % NQT, i = qt * QROWS + row, NK = keys_of(qt), NCH = NK / 32;
+            const int bh = w / NQT, qt = tile_of(w, n), i = qt * QROWS + row, NK = keys_of(qt), NCH = NK / 32;
+            // the warp's 32 rows of the row tensors: first row and the distance between rows (the tensors are affine in i)
+            const int iw = qt * QROWS + 32 * q;
+            float *r_base = F::STORE_R ? f.r_row(iw, bh) : nullptr;
+            const int r_rs = F::STORE_R ? (int)(f.r_row(iw + 1, bh) - f.r_row(iw, bh)) : 0;
+            float *e_base = (F::STORE_E || F::MODE == 1) ? f.e_row(iw, bh) : nullptr;
+            const int e_rs = (F::STORE_E || F::MODE == 1) ? (int)(f.e_row(iw + 1, bh) - f.e_row(iw, bh)) : 0;
+            const float *p_base = F::MODE == 1 ? f.p_row(iw, bh) : nullptr;
+            const int p_rs = F::MODE == 1 ? (int)(f.p_row(iw + 1, bh) - f.p_row(iw, bh)) : 0;
             if (F::MODE == 1) {                                                   // this row's p and e lines: on their way while product 1 runs
-                const float *pp = f.p_row(i, bh), *ep = f.e_row(i, bh);
-                for (int c = h; c < NCH; c += 2) { anvil::prefetch_l2(pp + 32 * c); anvil::prefetch_l2(ep + 32 * c); }
+                for (int c = h; c < NCH; c += 2) { anvil::prefetch_l2(p_base + lane * p_rs + 32 * c); anvil::prefetch_l2(e_base + lane * e_rs + 32 * c); }
             }
             // keys this tile cannot see: exp(-1e9 - m) = 0 exactly, so e, p and ds are zeros there; written while product 1 runs
             for (int c = NCH + h; c < T / 32; c += 2) {
-                if (F::STORE_R) {
-                    float *z = f.r_row(i, bh) + 32 * c;
-#pragma unroll
-                    for (int x = 0; x < 32; x += 4) *reinterpret_cast<float4 *>(z + x) = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                if (F::STORE_E && F::MODE == 0) {
-                    float *z = f.e_row(i, bh) + 32 * c;
-#pragma unroll
-                    for (int x = 0; x < 32; x += 4) *reinterpret_cast<float4 *>(z + x) = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
+                if (F::STORE_R) tile_zero32(lane, r_base + 32 * c, r_rs);
+                if (F::STORE_E && F::MODE == 0) tile_zero32(lane, e_base + 32 * c, e_rs);
             }
             bool ok = mbar_wait(s_full, (uint32_t)(n & 1));
             if (!ok) *rfail = 1;
             row_bar();
             if (*rfail) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float rowsum = 1.0f;
-            float *r_row = F::STORE_R ? f.r_row(i, bh) : nullptr;
+            float oscale = F::ALPHA2;                                              // what the epilogue multiplies this row of O by
             if (F::MODE == 0) {
-                // ---- forward: max, then exp and sum; e goes back into tensor memory in place
-                float m = -CUDART_INF_F;
+                // ---- forward: max; then e = exp(s - max), its sum, and e straight into product 2 (which therefore sums
+                // e * v; the division by the row sum is applied to its 64 results instead of to the T probabilities)
+                float m4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
                 for (int c = h; c < NCH; c += 2) {
                     uint32_t r[32];
                     tmem_ld32(lane_addr + COL_S + 32 * c, r);
 #pragma unroll
-                    for (int x = 0; x < 32; x++) m = anvil::fmax_nan(m, f.post(__uint_as_float(r[x]) * F::ALPHA1, i, 32 * c + x, bh));
+                    for (int x = 0; x < 32; x++) m4[x & 3] = anvil::fmax_nan(m4[x & 3], f.post(__uint_as_float(r[x]) * F::ALPHA1, i, 32 * c + x, bh));
                 }
-                red[h * 128 + row] = m;
+                red[h * 128 + row] = anvil::fmax_nan(anvil::fmax_nan(m4[0], m4[1]), anvil::fmax_nan(m4[2], m4[3]));
                 row_bar();
-                m = anvil::fmax_nan(red[row], red[128 + row]);
+                const float m = anvil::fmax_nan(red[row], red[128 + row]);
                 row_bar();
                 float sum = 0.0f;
-                float *e_row = F::STORE_E ? f.e_row(i, bh) : nullptr;
-                for (int c = h; c < NCH; c += 2) {
+                for (int c = h; c < NCH && ok; c += 2) {
                     uint32_t r[32];
                     tmem_ld32(lane_addr + COL_S + 32 * c, r);
 #pragma unroll
@@ -271,104 +348,104 @@ __device__ __forceinline__ void attn_fused(const F &f, uint32_t *status) {
                         sum = sum + e;
                         r[x] = __float_as_uint(e);
                     }
-                    tmem_st16_at(lane_addr + COL_S + 32 * c, r);
-                    tmem_st16_at(lane_addr + COL_S + 32 * c + 16, r + 16);
-                    if (F::STORE_E) store32(e_row + 32 * c, r);
+                    if (F::STORE_R) {                                              // kept in place for the pass that writes p
+                        tmem_st16_at(lane_addr + COL_S + 32 * c, r);
+                        tmem_st16_at(lane_addr + COL_S + 32 * c + 16, r + 16);
+                    }
+                    if (F::STORE_E) tile_store<32>(stage_f, lane, e_base + 32 * c, e_rs, r);
+                    ok = feed_begin();
+                    if (ok) { feed_half(0, r); feed_half(1, r + 16); feed_end(); }
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 red[h * 128 + row] = sum;
                 row_bar();
-                rowsum = red[row] + red[128 + row];
+                const float rowsum = red[row] + red[128 + row];
                 row_bar();
+                const float rinv = 1.0f / rowsum;                                  // e / sum as e * (1 / sum)
+                oscale = rinv * F::ALPHA2;
                 if (h == 0) {
                     if (F::STORE_SUM) *f.sum_at(i, bh) = rowsum;
                     if (F::STORE_MAX) *f.max_at(i, bh) = m;
                 }
+                if (F::STORE_R) {                                                  // p = e / sum, for the kernels that read it later
+                    for (int c = h; c < NCH; c += 2) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_addr + COL_S + 32 * c, r);
+#pragma unroll
+                        for (int x = 0; x < 32; x++) r[x] = __float_as_uint(__uint_as_float(r[x]) * rinv);
+                        tile_store<32>(stage_f, lane, r_base + 32 * c, r_rs, r);
+                    }
+                }
             } else {
-                // ---- backward: dt = sum_j dp * (-p / sum); then ds = (dp / sum + dt) * e, back into tensor memory in place
+                // ---- backward: dt = sum_j dp * (-p / sum); then ds = (dp / sum + dt) * e, to memory and into product 2
                 const float tsum = *f.sum_at(i, bh);
-                const float *p_row = f.p_row(i, bh), *e_row = f.e_row(i, bh);
                 const float ninv = -1.0f / tsum;                                   // -p / sum as p * (-1 / sum): one rounding more, no division per element
                 float dt = 0.0f;
-                for (int c = h; c < NCH; c += 2) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_addr + COL_S + 32 * c, r);
+                // 16 columns at a time (the registers hold two operands), the next tile's loads in flight during the work on this one
+                auto next_of = [](int c2) { return c2 + ((c2 & 1) ? 3 : 1); };     // this warp's half chunks: 2h, 2h + 1, 2h + 4, 2h + 5, ..
+                float4 raw[4];
+                tile_fetch16(lane, p_base + 16 * (2 * h), p_rs, raw);
+                for (int c2 = 2 * h; c2 < 2 * NCH; c2 = next_of(c2)) {
+                    uint32_t r[16];
+                    float pv[16];
+                    tmem_ld16(lane_addr + COL_S + 16 * c2, r);
+                    tile_hand_over16(stage_f, lane, raw, pv);
+                    if (next_of(c2) < 2 * NCH) tile_fetch16(lane, p_base + 16 * next_of(c2), p_rs, raw);
+                    else tile_fetch16(lane, e_base + 16 * (2 * h), e_rs, raw);   // the second pass's first tile
 #pragma unroll
-                    for (int x = 0; x < 32; x += 4) {
-                        const float4 pv = *reinterpret_cast<const float4 *>(p_row + 32 * c + x);
-                        dt = dt + (__uint_as_float(r[x]) * F::ALPHA1) * (pv.x * ninv);
-                        dt = dt + (__uint_as_float(r[x + 1]) * F::ALPHA1) * (pv.y * ninv);
-                        dt = dt + (__uint_as_float(r[x + 2]) * F::ALPHA1) * (pv.z * ninv);
-                        dt = dt + (__uint_as_float(r[x + 3]) * F::ALPHA1) * (pv.w * ninv);
-                    }
+                    for (int x = 0; x < 16; x++) dt = dt + (__uint_as_float(r[x]) * F::ALPHA1) * (pv[x] * ninv);
                 }
                 red[h * 128 + row] = dt;
                 row_bar();
                 dt = red[row] + red[128 + row];
                 row_bar();
                 const float inv = 1.0f / tsum;
-                for (int c = h; c < NCH; c += 2) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_addr + COL_S + 32 * c, r);
+                for (int c2 = 2 * h; c2 < 2 * NCH; c2 = next_of(c2)) {
+                    if (!(c2 & 1)) { ok = feed_begin(); if (!ok) break; }
+                    uint32_t r[16];
+                    float ev[16];
+                    tmem_ld16(lane_addr + COL_S + 16 * c2, r);
+                    tile_hand_over16(stage_f, lane, raw, ev);
+                    if (next_of(c2) < 2 * NCH) tile_fetch16(lane, e_base + 16 * next_of(c2), e_rs, raw);
 #pragma unroll
-                    for (int x = 0; x < 32; x += 4) {
-                        const float4 ev = *reinterpret_cast<const float4 *>(e_row + 32 * c + x);
-                        r[x] = __float_as_uint(((__uint_as_float(r[x]) * F::ALPHA1) * inv + dt) * ev.x);
-                        r[x + 1] = __float_as_uint(((__uint_as_float(r[x + 1]) * F::ALPHA1) * inv + dt) * ev.y);
-                        r[x + 2] = __float_as_uint(((__uint_as_float(r[x + 2]) * F::ALPHA1) * inv + dt) * ev.z);
-                        r[x + 3] = __float_as_uint(((__uint_as_float(r[x + 3]) * F::ALPHA1) * inv + dt) * ev.w);
-                    }
-                    tmem_st16_at(lane_addr + COL_S + 32 * c, r);
-                    tmem_st16_at(lane_addr + COL_S + 32 * c + 16, r + 16);
+                    for (int x = 0; x < 16; x++) r[x] = __float_as_uint(((__uint_as_float(r[x]) * F::ALPHA1) * inv + dt) * ev[x]);
+                    if (F::STORE_R) tile_store<16>(stage_f, lane, r_base + 16 * c2, r_rs, r);
+                    feed_half(c2 & 1, r);
+                    if (c2 & 1) feed_end();
                 }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            }
-            // ---- the row result: to memory (if somebody reads it later) and, split hi / lo, into stage h of product 2's A operand
-            for (int c = h; c < NCH && ok; c += 2) {
-                if (!mbar_wait(p_free(h), (fcount & 1u) ^ 1u)) { ok = false; break; }
-                fcount++;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t r[32], part[16];
-                tmem_ld32(lane_addr + COL_S + 32 * c, r);
-                if (F::MODE == 0) {
-                    const float rinv = 1.0f / rowsum;                                  // e / sum as e * (1 / sum)
-#pragma unroll
-                    for (int x = 0; x < 32; x++) r[x] = __float_as_uint(__uint_as_float(r[x]) * rinv);
-                }
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-#pragma unroll
-                    for (int x = 0; x < 16; x++) part[x] = r[16 * half + x] & 0xFFFFE000u;
-                    tmem_st16_at(lane_addr + COL_R + 64u * h + 16u * half, part);
-#pragma unroll
-                    for (int x = 0; x < 16; x++) part[x] = __float_as_uint(__uint_as_float(r[16 * half + x]) - __uint_as_float(part[x]));
-                    tmem_st16_at(lane_addr + COL_R + 64u * h + 32u + 16u * half, part);
-                }
-                if (F::STORE_R) store32(r_row + 32 * c, r);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full(h));
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);                                    // the next tile's product 1 may overwrite S
-            // ---- epilogue of product 2: the first warp of each lane quarter takes its 32 rows of O (shared memory for the
-            // transposition is short: the operand tiles take nearly all of it)
+            // ---- epilogue of product 2: warp (q, h) takes rows 32 q .. 32 q + 31, columns 32 h .. 32 h + 31 of O = the sum of
+            // the two accumulators (even and odd key chunks), 16 rows at a time through shared memory for coalesced stores
             if (!ok || !mbar_wait(o_full, (uint32_t)(n & 1))) *rfail = 1;
             row_bar();
             if (*rfail) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int c = 0; c < DH / 32 && h == 0; c++) {
-                uint32_t r[32];
-                tmem_ld32(lane_addr + COL_O + 32 * c, r);
+            static_assert(DH / 32 == ROW_WARPS / 4, "one 32-column chunk of O per warp of a lane quarter");
+            {
+                float o[32];
 #pragma unroll
-                for (int x = 0; x < 32; x++) stage_f[lane * 33 + x] = __uint_as_float(r[x]);
-                __syncwarp();
+                for (int hc = 0; hc < 2; hc++) {                                   // 16 columns at a time: fewer registers live
+                    uint32_t ra[16], rb[16];
+                    tmem_ld16(lane_addr + COL_O + 32 * h + 16 * hc, ra);
+                    tmem_ld16(lane_addr + COL_O + 64 + 32 * h + 16 * hc, rb);
+#pragma unroll
+                    for (int x = 0; x < 16; x++) o[16 * hc + x] = (__uint_as_float(ra[x]) + __uint_as_float(rb[x])) * oscale;
+                }
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    if ((lane >> 4) == half) {
+#pragma unroll
+                        for (int x = 0; x < 32; x++)
+                            stage_f[(lane & 15) * 36 + x] = o[x];
+                    }
+                    __syncwarp();
 #pragma unroll 4
-                for (int rr = 0; rr < 32; rr++)
-                    f.epi(qt * QROWS + 32 * q + rr, 32 * c + lane, bh, stage_f[rr * 33 + lane] * F::ALPHA2);
-                __syncwarp();
+                    for (int rr = 0; rr < 16; rr++)
+                        f.epi(qt * QROWS + 32 * q + 16 * half + rr, 32 * h + lane, bh, stage_f[rr * 36 + lane]);
+                    __syncwarp();
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }

@@ -113,25 +113,8 @@ struct TileMap {
     }
 };
 
-#ifndef ANVIL_TC_RAW_HI
-#define ANVIL_TC_RAW_HI 0
-#endif
 __device__ __forceinline__ void split_store(uint8_t *hi_tile, uint8_t *lo_tile, uint32_t off, const float (&v)[4]) {
     float4 hi, lo;
-#if ANVIL_TC_RAW_HI
-    {   // experiment: the hi tile holds the raw f32 (the tensor core reads its top 19 bits); lo against truncation (1) or rounding (2)
-        float h[4];
-        for (int z = 0; z < 4; z++) {
-            if (ANVIL_TC_RAW_HI == 1) h[z] = __uint_as_float(__float_as_uint(v[z]) & 0xFFFFE000u);
-            else { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[z])); h[z] = __uint_as_float(u); }
-        }
-        hi = make_float4(v[0], v[1], v[2], v[3]);
-        lo = make_float4(v[0] - h[0], v[1] - h[1], v[2] - h[2], v[3] - h[3]);
-        *reinterpret_cast<float4 *>(hi_tile + off) = hi;
-        *reinterpret_cast<float4 *>(lo_tile + off) = lo;
-        return;
-    }
-#endif
     hi.x = __uint_as_float(__float_as_uint(v[0]) & 0xFFFFE000u); lo.x = v[0] - hi.x;
     hi.y = __uint_as_float(__float_as_uint(v[1]) & 0xFFFFE000u); lo.y = v[1] - hi.y;
     hi.z = __uint_as_float(__float_as_uint(v[2]) & 0xFFFFE000u); lo.z = v[2] - hi.z;
