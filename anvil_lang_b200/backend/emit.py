@@ -2167,6 +2167,10 @@ def generate(prog: kir.Program, seed: int = 0):
     if os_environ("ANVIL_B200_REFUSE", "1") != "0":
         from .refuse import fuse_consumers
         fuse_consumers(prog)                         # optimizer updates join the kernel that makes their gradient (idempotent)
+    if os_environ("ANVIL_B200_REMAT", "1") != "0":
+        from .refuse import _host_reads
+        from .remat import rematerialize
+        rematerialize(prog, _host_reads(prog))       # saved elementwise intermediates are recomputed where they are read (idempotent)
     g = ProgramGen(prog, seed)
     src = g.generate()
     if g.scratch_bytes > g.plan.scratch_bytes:
