@@ -791,10 +791,7 @@ class KernelGen:
         for i in range(4):
             tree.append(f"{ind}acc_{i} = sm_[0][4 * ox + {i}];")
         lines.append(f"{ind}float *part_ = (float *)(A + {soff}UL);")
-        lines.append(f"{ind}if (ry == 0 && live) {{")
-        for i in range(4):
-            lines.append(f"{ind}    part_[blockIdx.y * {ON}L + o_ * 4 + {i}] = acc_{i};")
-        lines.append(f"{ind}}}")
+        lines.append(f"{ind}if (ry == 0 && live) *reinterpret_cast<float4 *>(part_ + blockIdx.y * {ON}L + o_ * 4) = make_float4(acc_0, acc_1, acc_2, acc_3);")
         lines += [f"{ind}__threadfence();", f"{ind}__shared__ unsigned last_;", f"{ind}__syncthreads();",
                   f"{ind}unsigned *ticket_ = (unsigned *)(A + ANVIL_RT_TICKETS_OFF) + blockIdx.x;",
                   f"{ind}if (threadIdx.x == 0) last_ = atomicAdd(ticket_, 1u) == {S - 1}u;",
@@ -802,10 +799,11 @@ class KernelGen:
         for i in range(4):
             lines.append(f"{ind}acc_{i} = {OP}::id<float>();")
         lines.append(f"{ind}if (live) {{")
-        lines.append("#pragma unroll 4")
+        lines.append("#pragma unroll 16")               # all of a thread's partials in flight at once: one trip to L2
         lines.append(f"{ind}    for (int p = ry; p < {S}; p += {RY}) {{")
-        for i in range(4):
-            lines.append(f"{ind}        acc_{i} = {OP}::f(acc_{i}, __ldcg(part_ + p * {ON}L + o_ * 4 + {i}));")
+        lines.append(f"{ind}        const float4 q_ = __ldcg(reinterpret_cast<const float4 *>(part_ + p * {ON}L + o_ * 4));")
+        for i, c in enumerate("xyzw"):
+            lines.append(f"{ind}        acc_{i} = {OP}::f(acc_{i}, q_.{c});")
         lines.append(f"{ind}    }}")
         lines.append(f"{ind}}}")
         lines.append(f"{ind}__syncthreads();")
@@ -2171,6 +2169,9 @@ def generate(prog: kir.Program, seed: int = 0):
         from .refuse import _host_reads
         from .remat import rematerialize
         rematerialize(prog, _host_reads(prog))       # saved elementwise intermediates are recomputed where they are read (idempotent)
+    if os_environ("ANVIL_B200_REFUSE", "1") == "all":
+        from .refuse import fuse_consumers
+        fuse_consumers(prog, only_updates=False)     # every elementwise consumer joins the kernel that makes its input
     g = ProgramGen(prog, seed)
     src = g.generate()
     if g.scratch_bytes > g.plan.scratch_bytes:
