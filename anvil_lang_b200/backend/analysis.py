@@ -165,6 +165,82 @@ class ArenaPlan:
         return self.shared | self.unused
 
 
+SIDE_MAX_FLOPS = 4_000_000_000           # larger kernels (the contractions) stay on the main stream
+
+
+def _stmt_roots(st) -> tuple[set, set]:
+    """(root ids read, root ids written) by a statement and everything nested in it; a runtime call or a collective
+    counts as reading and writing every tensor it names."""
+    r: set = set()
+    w: set = set()
+
+    def buf(b, write=False):
+        if isinstance(b, kir.Buffer):
+            (w if write else r).add(b.root.id)
+    if isinstance(st, kir.KernelStmt):
+        return {b.id for b in st.kernel.reads()}, {b.id for b in st.kernel.writes()}
+    if isinstance(st, kir.Print):
+        for it in st.items:
+            buf(it.buf)
+    elif isinstance(st, kir.Check):
+        for t, _ in st.value.scalars():
+            buf(t.buf)
+    elif isinstance(st, kir.RTCall):
+        for v in st.args.values():
+            for x in (v if isinstance(v, list) else [v]):
+                buf(x); buf(x, True)
+    elif isinstance(st, kir.AllReduce):
+        for b in st.bufs:
+            buf(b); buf(b, True)
+    elif isinstance(st, kir.For):
+        buf(st.start); buf(st.stop); buf(st.counter); buf(st.counter, True)
+    elif isinstance(st, (kir.While, kir.If)):
+        buf(st.cond)
+    for name in ("body", "then", "orelse", "cond_block"):
+        blk = getattr(st, name, None)
+        if isinstance(blk, kir.Block):
+            for inner in blk.stmts:
+                r2, w2 = _stmt_roots(inner)
+                r |= r2
+                w |= w2
+    return r, w
+
+
+def deferred_kernels(prog: kir.Program) -> set:
+    """Ids of kernels inside loops whose results nothing in the rest of their statement list needs: the rest neither
+    reads nor writes what they write, and does not write what they read. They are the updates of biases, gains and
+    their optimizer state at the end of a training step. Such a kernel may run on a second stream beside the kernels
+    that follow it, as long as it has finished when the list ends. Kernels that draw random numbers (their stream
+    position is ordered) and large ones (contractions want the whole GPU) are left out."""
+    out: set = set()
+
+    def visit(block: kir.Block, in_loop: bool):
+        stmts = block.stmts
+        if in_loop:
+            later_r: set = set()
+            later_w: set = set()
+            for st in reversed(stmts):
+                r, w = _stmt_roots(st)
+                if isinstance(st, kir.KernelStmt):
+                    k = st.kernel
+                    if (not k.uses_rand() and k.rand_base is None and kernel_flops(k) <= SIDE_MAX_FLOPS
+                            and not (w & (later_r | later_w)) and not (r & later_w)):
+                        out.add(k.id)
+                later_r |= r
+                later_w |= w
+        for st in stmts:
+            if isinstance(st, kir.For):
+                visit(st.body, True)
+            elif isinstance(st, kir.While):
+                visit(st.cond_block, True)
+                visit(st.body, True)
+            elif isinstance(st, kir.If):
+                visit(st.then, in_loop)
+                visit(st.orelse, in_loop)
+    visit(prog.main, False)
+    return out
+
+
 SHARED_KINDS = ("temp", "grad")
 FULL_WRITE_CALLS = ("nonzero", "input", "clock", "iota", "iota_once")
 MIN_SHARED_BYTES = 4096                  # smaller tensors keep their own memory: nothing to gain
@@ -190,11 +266,12 @@ class _Use:
         self.pos, self.chain, self.write, self.full, self.after = pos, chain, write, full, after
 
 
-def _flatten(prog: kir.Program, fused_runs):
+def _flatten(prog: kir.Program, fused_runs, deferred=()):
     """Every use of every root buffer with its statement position and the loops / branches around it, and the
     position ranges of the loops (the walk of anvil/backend/arena.py:36-98 over this IR). `fused_runs(kernels)` gives
     index ranges of consecutive kernels that the emitter runs as ONE kernel: they share a position, so nothing
-    one of them reads can give its bytes to something another one writes."""
+    one of them reads can give its bytes to something another one writes. `deferred`: ids of kernels that may still be
+    running on a second stream until the end of their run of kernels: what they touch is in use until then."""
     uses: dict = {}
     loops: list = []
     pos = 0
@@ -233,6 +310,12 @@ def _flatten(prog: kir.Program, fused_runs):
                     for k in run[q:end]:
                         kernel_uses(k, chain, seen_full)
                     q = end
+                late = [k for k in run if k.id in deferred]
+                if late:
+                    pos += 1                         # the join
+                    for k in late:
+                        for r in list(k.reads()) + list(k.writes()):
+                            note(r, chain)
                 i = j
                 continue
             stmt(st, chain)
@@ -306,18 +389,22 @@ def _lifetime(us, loops):
     return lo, hi
 
 
-def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256 + 4 * 256, share: bool = True, fused_runs=None,
-               keep=()) -> ArenaPlan:
+def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256 + 2 * 4 * 256, share: bool = True, fused_runs=None,
+               keep=(), deferred=(), side_scratch_bytes: int = 0) -> ArenaPlan:
     """One arena for the whole program. Temporaries (`temp`, `grad`) whose first use writes all of them and whose
     lifetimes do not overlap share bytes (first fit by decreasing size, ids break ties: the layout is the same every
     run, like anvil/backend/arena.py:121-144); tensors nothing touches get no memory; every other root buffer
     gets its own zero-initialised, 256-byte aligned region (the reference gives each its own zeroed allocation,
-    anvil/backend/cuda.py:416-421). `keep`: root ids that must not share (tensors the host reads or feeds)."""
+    anvil/backend/cuda.py:416-421). `keep`: root ids that must not share (tensors the host reads or feeds).
+    `deferred` / `side_scratch_bytes`: kernels that run on the second stream (see `deferred_kernels`) and the scratch
+    space of their own that split reductions among them need (they run beside main-stream kernels that use the first)."""
     def up(n):
         return (n + ALIGN - 1) // ALIGN * ALIGN
     pos = up(header)
     scratch_off = pos
     pos += up(max(scratch_bytes, 4))
+    side_scratch_off = pos
+    pos += up(max(side_scratch_bytes, 4))
     offsets = {}
     bucket = [b.root for b in getattr(prog, "bucket", [])]
     bucket_off = pos
@@ -328,7 +415,8 @@ def plan_arena(prog: kir.Program, scratch_bytes: int = 0, header: int = 256 + 4 
     bucket_bytes = pos - bucket_off
     plan = ArenaPlan(offsets, 0, scratch_off, up(max(scratch_bytes, 4)))
     plan.bucket_off, plan.bucket_bytes = bucket_off, bucket_bytes
-    uses, loops = _flatten(prog, fused_runs)
+    plan.side_scratch_off, plan.side_scratch_bytes = side_scratch_off, up(max(side_scratch_bytes, 4))
+    uses, loops = _flatten(prog, fused_runs, deferred)
     roots = prog.roots()
     items = []
     if share:

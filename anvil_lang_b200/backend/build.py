@@ -114,7 +114,8 @@ def load_runtime() -> ctypes.CDLL:
     sig = {
         "anvil_rt_create": (P, [I]), "anvil_rt_destroy": (None, [P]), "anvil_rt_arena": (I, [P, Z]),
         "anvil_rt_ptr": (P, [P, Z]), "anvil_rt_arena_bytes": (Z, [P]), "anvil_rt_stream": (P, [P]),
-        "anvil_rt_use_stream": (I, [P, P]), "anvil_rt_last_error": (c.c_char_p, [P]),
+        "anvil_rt_use_stream": (I, [P, P]), "anvil_rt_fork": (I, [P]), "anvil_rt_back": (I, [P]), "anvil_rt_join": (I, [P]),
+        "anvil_rt_side_stream": (I, [P, I]), "anvil_rt_last_error": (c.c_char_p, [P]),
         "anvil_rt_set_error": (I, [P, c.c_char_p]),
         "anvil_rt_load_idx": (I, [P, c.c_char_p, Z, L, L, I]), "anvil_rt_load_csv": (I, [P, c.c_char_p, Z, L, L]),
         "anvil_rt_load_bytes": (I, [P, c.c_char_p, Z, L]), "anvil_rt_input": (I, [P, Z, c.POINTER(I)]),

@@ -530,6 +530,19 @@ class KernelGen:
             return self.gen_coop_col4(base, *choice[1:])
         return self.gen_coop(base, *choice[1:])
 
+    @property
+    def side(self) -> bool:
+        """Does this kernel run on the second stream, beside main-stream kernels? Then partial sums and tickets of a
+        split reduction go to a scratch region and counters of their own."""
+        return self.k.id in self.gen.side_ids
+
+    def scratch(self, nbytes: int) -> int:
+        if self.side:
+            self.gen.side_scratch_bytes = max(self.gen.side_scratch_bytes, nbytes)
+            return self.gen.plan.side_scratch_off
+        self.gen.need_scratch(nbytes)
+        return self.gen.plan.scratch_off
+
     def launch_line(self, name, blocks, threads) -> str:
         return (f"{name}<<<{blocks}, {threads}, 0, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
 
@@ -688,8 +701,7 @@ class KernelGen:
             self.notes = f"coop {layout} {OX}x{RY} L{L}"
             return "\n".join(src), launch
         # split: partial results to scratch, second kernel combines them in order and runs the statements
-        self.gen.need_scratch(4 * ON * S)
-        soff = self.gen.plan.scratch_off
+        soff = self.scratch(4 * ON * S)
         lines.append(f"{ind}if (ry == 0 && live) (({T} *)(A + {soff}UL))[blockIdx.y * {ON}L + o_] = acc;")   # [slice][output]
         part = [self.comment(f"split reduction, part 1 of 2 ({layout}, {S} CTAs per output group)"),
                 self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
@@ -775,8 +787,7 @@ class KernelGen:
         # sums to scratch and takes a ticket; the last one adds all S partials in a fixed order (slice ry takes partials
         # ry, ry + RY, ..., then the same shared-memory tree) and runs the statements. The result does not depend on which
         # CTA is last, and there is no second launch.
-        self.gen.need_scratch(4 * ON * S)
-        soff = self.gen.plan.scratch_off
+        soff = self.scratch(4 * ON * S)
         assert gx <= 256, "ticket counters"
         tree = []
         for i in range(4):
@@ -793,7 +804,7 @@ class KernelGen:
         lines.append(f"{ind}float *part_ = (float *)(A + {soff}UL);")
         lines.append(f"{ind}if (ry == 0 && live) *reinterpret_cast<float4 *>(part_ + blockIdx.y * {ON}L + o_ * 4) = make_float4(acc_0, acc_1, acc_2, acc_3);")
         lines += [f"{ind}__threadfence();", f"{ind}__shared__ unsigned last_;", f"{ind}__syncthreads();",
-                  f"{ind}unsigned *ticket_ = (unsigned *)(A + ANVIL_RT_TICKETS_OFF) + blockIdx.x;",
+                  f"{ind}unsigned *ticket_ = (unsigned *)(A + {'ANVIL_RT_SIDE_TICKETS_OFF' if self.side else 'ANVIL_RT_TICKETS_OFF'}) + blockIdx.x;",
                   f"{ind}if (threadIdx.x == 0) last_ = atomicAdd(ticket_, 1u) == {S - 1}u;",
                   f"{ind}__syncthreads();", f"{ind}if (!last_) return;", f"{ind}__threadfence();"]
         for i in range(4):
@@ -1107,6 +1118,11 @@ class KernelGen:
 def os_environ(name: str, default: str) -> str:
     import os
     return os.environ.get(name, default)
+
+
+def use_side_stream() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_SIDE", "1") != "0"
 
 
 def use_attention() -> bool:
@@ -1594,6 +1610,9 @@ class ProgramGen:
         self.seed = seed & 0xFFFFFFFF
         self.faults: list[str] = []
         self.scratch_bytes = 4
+        self.side_scratch_bytes = 4
+        self.deferred = an.deferred_kernels(prog) if use_side_stream() else set()
+        self.side_ids: set = set()                   # deferred kernels that are launch units of their own: they run on the second stream
         self.readers: dict = {}
         for k in prog.kernels():
             for r in k.reads():
@@ -1623,7 +1642,7 @@ class ProgramGen:
         self.record_units = False
         self.host_read = self._host_reads()
 
-    def make_plan(self, scratch_bytes: int):
+    def make_plan(self, scratch_bytes: int, side_scratch_bytes: int = 4):
         """The arena plan: lifetime sharing unless ANVIL_B200_ARENA=unshared. Tensors the host reads (printed values,
         loop conditions, checkpoints) or feeds (the step's inputs) keep their own memory, so they can be read between
         steps; row kernels that will run as one fused kernel count as one statement."""
@@ -1636,7 +1655,7 @@ class ProgramGen:
             spans = at.find_attention(ks, self.readers, host, self.causal_e) if use_attention() else []
             return fused_runs(ks, spans)
         return an.plan_arena(self.prog, scratch_bytes, share=os_environ("ANVIL_B200_ARENA", "shared") != "unshared",
-                             fused_runs=runs, keep=keep)
+                             fused_runs=runs, keep=keep, deferred=self.deferred, side_scratch_bytes=side_scratch_bytes)
 
     def _host_reads(self) -> set:
         """Root ids of tensors that something other than a kernel reads."""
@@ -1840,11 +1859,7 @@ class ProgramGen:
                 run_kernels = []
                 while j < len(stmts) and isinstance(stmts[j], kir.KernelStmt):
                     kj = stmts[j].kernel
-                    self.add_kernel(kj)
-                    if kj.id in skip:                # fed from the host; its random stream is still consumed
-                        if kj.uses_rand():
-                            calls.append("anvil_rt_set_stream(rt, anvil_rt_get_stream(rt) + 1u);")
-                    else:
+                    if kj.id not in skip:
                         run_kernels.append(kj)
                     j += 1
                 spans = rg.find_groups(run_kernels) if use_row_groups() else []
@@ -1852,6 +1867,26 @@ class ProgramGen:
                 hstarts = {a: (b, kind) for a, b, kind in (hfuse.find_hgroups(run_kernels, tc_eligible_pp) if use_hgroups() else [])}
                 astarts = {a: (b, g) for a, b, g in (at.find_attention(run_kernels, self.readers, self.host_read, self.causal_e)
                                                        if use_attention() else [])}
+                if in_loop:                          # deferred kernels that stay launch units of their own go to the second stream
+                    q = 0
+                    while q < len(run_kernels):
+                        if q in astarts:
+                            q = astarts[q][0]
+                        elif q in hstarts:
+                            q = hstarts[q][0]
+                        elif q in starts:
+                            q = starts[q]
+                        else:
+                            kq = run_kernels[q]          # (decided once, before the kernel's source exists; contractions stay)
+                            if kq.id in self.deferred and kq.id not in self.kernel_index and ct.match(kq) is None:
+                                self.side_ids.add(kq.id)
+                            q += 1
+                for x in stmts[i:j]:
+                    kj = x.kernel
+                    self.add_kernel(kj)
+                    if kj.id in skip and kj.uses_rand():      # fed from the host; its random stream is still consumed
+                        calls.append("anvil_rt_set_stream(rt, anvil_rt_get_stream(rt) + 1u);")
+                forked = False
                 q = 0
                 while q < len(run_kernels):
                     if q in astarts:
@@ -1879,10 +1914,16 @@ class ProgramGen:
                     else:
                         idx = self.kernel_index[run_kernels[q].id]
                         run.append(idx)
-                        calls.append(f"RT(launch_{idx}(rt));")
+                        if run_kernels[q].id in self.side_ids:
+                            calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_{idx}(rt)); anvil_rt_back(rt);")
+                            forked = True
+                        else:
+                            calls.append(f"RT(launch_{idx}(rt));")
                         if self.record_units:
                             self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
                         q += 1
+                if forked:
+                    calls.append("RT(anvil_rt_join(rt));")
                 if j == len(stmts) and tail is not None:
                     calls += tail
                     tail_done = True
@@ -2174,10 +2215,10 @@ def generate(prog: kir.Program, seed: int = 0):
         fuse_consumers(prog, only_updates=False)     # every elementwise consumer joins the kernel that makes its input
     g = ProgramGen(prog, seed)
     src = g.generate()
-    if g.scratch_bytes > g.plan.scratch_bytes:
-        need = g.scratch_bytes
+    if g.scratch_bytes > g.plan.scratch_bytes or g.side_scratch_bytes > g.plan.side_scratch_bytes:
+        need, side_need = g.scratch_bytes, g.side_scratch_bytes
         g = ProgramGen(prog, seed)
-        g.plan = g.make_plan(need)
-        g.scratch_bytes = need
+        g.plan = g.make_plan(need, side_need)
+        g.scratch_bytes, g.side_scratch_bytes = need, side_need
         src = g.generate()
     return src, g

@@ -57,6 +57,14 @@ struct anvil_rt {
     cudaEvent_t pe0 = nullptr, pe1 = nullptr;
     char *stage[2] = {nullptr, nullptr};        // pinned staging buffers for large copies from / to pageable host memory
     cudaEvent_t stage_ev[2] = {nullptr, nullptr};
+    // second stream: kernels whose results nothing in the rest of their launch run needs (parameter updates of small
+    // tensors) run beside the kernels that follow them; fork / join are event edges, which a stream capture records
+    // as graph dependencies
+    cudaStream_t side = nullptr;
+    cudaStream_t current = nullptr;             // what launches go to; nullptr = `stream`
+    cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+    bool forked = false;
+    bool side_on = true;
 };
 
 static double now_seconds() {
@@ -95,6 +103,12 @@ extern "C" anvil_rt *anvil_rt_create(int device) {
         rt->error = std::string("anvil: CUDA error: ") + cudaGetErrorString(cudaGetLastError());
         rt->stream = nullptr;
     }
+    if (rt->stream && (cudaStreamCreateWithFlags(&rt->side, cudaStreamNonBlocking) != cudaSuccess ||
+                       cudaEventCreateWithFlags(&rt->fork_ev, cudaEventDisableTiming) != cudaSuccess ||
+                       cudaEventCreateWithFlags(&rt->join_ev, cudaEventDisableTiming) != cudaSuccess)) {
+        cudaGetLastError();
+        rt->side = nullptr;                      // no second stream: everything runs on the first
+    }
     return rt;
 }
 
@@ -108,6 +122,9 @@ extern "C" void anvil_rt_destroy(anvil_rt *rt) {
     if (rt->ev0) { cudaEventDestroy(rt->ev0); cudaEventDestroy(rt->ev1); }
     if (rt->pe0) { cudaEventDestroy(rt->pe0); cudaEventDestroy(rt->pe1); }
     for (int i = 0; i < 2; i++) { if (rt->stage[i]) cudaFreeHost(rt->stage[i]); if (rt->stage_ev[i]) cudaEventDestroy(rt->stage_ev[i]); }
+    if (rt->side) { cudaStreamSynchronize(rt->side); cudaStreamDestroy(rt->side); }
+    if (rt->fork_ev) cudaEventDestroy(rt->fork_ev);
+    if (rt->join_ev) cudaEventDestroy(rt->join_ev);
     if (rt->stream && rt->own_stream) cudaStreamDestroy(rt->stream);
     delete rt;
 }
@@ -127,7 +144,29 @@ extern "C" int anvil_rt_arena(anvil_rt *rt, size_t bytes) {
 
 extern "C" void *anvil_rt_ptr(anvil_rt *rt, size_t off) { return rt->arena + off; }
 extern "C" size_t anvil_rt_arena_bytes(anvil_rt *rt) { return rt->arena_bytes; }
-extern "C" void *anvil_rt_stream(anvil_rt *rt) { return (void *)rt->stream; }
+extern "C" void *anvil_rt_stream(anvil_rt *rt) { return (void *)(rt->current ? rt->current : rt->stream); }
+
+// The next launches go to the second stream, ordered after everything issued on the first so far. With --profile or
+// --check (every launch unit is timed or scanned on the first stream) or without a second stream this is a no-op.
+extern "C" int anvil_rt_fork(anvil_rt *rt) {
+    if (!rt->side || !rt->side_on || rt->profile || rt->check) return 0;
+    CK(rt, cudaEventRecord(rt->fork_ev, rt->stream));
+    CK(rt, cudaStreamWaitEvent(rt->side, rt->fork_ev, 0));
+    rt->current = rt->side;
+    rt->forked = true;
+    return 0;
+}
+extern "C" int anvil_rt_back(anvil_rt *rt) { rt->current = nullptr; return 0; }
+// The first stream waits for what the second one was given since the last join.
+extern "C" int anvil_rt_join(anvil_rt *rt) {
+    rt->current = nullptr;
+    if (!rt->forked) return 0;
+    rt->forked = false;
+    CK(rt, cudaEventRecord(rt->join_ev, rt->side));
+    CK(rt, cudaStreamWaitEvent(rt->stream, rt->join_ev, 0));
+    return 0;
+}
+extern "C" int anvil_rt_side_stream(anvil_rt *rt, int on) { rt->side_on = on != 0; return 0; }
 extern "C" int anvil_rt_use_stream(anvil_rt *rt, void *s) {
     if (rt->stream && rt->own_stream) { cudaStreamSynchronize(rt->stream); cudaStreamDestroy(rt->stream); }
     rt->stream = (cudaStream_t)s;

@@ -33,6 +33,7 @@ extern "C" {
 #define ANVIL_RT_TICKETS_OFF 256    /* 256 x uint32 after the header: arrival counters of split reductions that finish in
                                        their last CTA; zero between launches                                       */
 #define ANVIL_RT_TICKETS 256
+#define ANVIL_RT_SIDE_TICKETS_OFF 1280 /* the same again for kernels on the second stream (they run beside kernels on the first) */
 
 typedef struct anvil_rt anvil_rt;
 
@@ -46,6 +47,14 @@ void *anvil_rt_ptr(anvil_rt *rt, size_t off);                 /* device address 
 size_t anvil_rt_arena_bytes(anvil_rt *rt);
 void *anvil_rt_stream(anvil_rt *rt);                          /* the context's cudaStream_t        */
 int anvil_rt_use_stream(anvil_rt *rt, void *cuda_stream);     /* run on a caller-owned stream      */
+/* Second stream (no reference counterpart: the reference launches on the default stream, anvil/backend/cuda.py:560-575).
+ * fork: the launches that follow go to the second stream, after everything issued so far; back: launches go to the
+ * first stream again; join: the first stream waits for the second. anvil_rt_stream() names the stream launches go to.
+ * A generated program forks for kernels whose results the rest of its launch run does not need and joins at its end. */
+int anvil_rt_fork(anvil_rt *rt);
+int anvil_rt_back(anvil_rt *rt);
+int anvil_rt_join(anvil_rt *rt);
+int anvil_rt_side_stream(anvil_rt *rt, int on);                /* 0: fork becomes a no-op            */
 const char *anvil_rt_last_error(anvil_rt *rt);
 int anvil_rt_set_error(anvil_rt *rt, const char *message);    /* returns 1                         */
 
