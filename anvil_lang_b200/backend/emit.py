@@ -398,8 +398,24 @@ class KernelGen:
         return out
 
     def head(self, name, threads) -> str:
+        """Opens the kernel. Bodies index their CTA through bx_ / by_ / gdx_ (block index and grid width): a kernel that is a
+        member of a side-by-side launch (`ZGroupGen`) is a device function that gets them as arguments, plus a thin
+        __global__ wrapper so it can still be launched alone."""
+        self.nthreads = threads
+        if self.member:
+            return (f"__device__ __forceinline__ void {name}_body(char *__restrict__ A, uint32_t sdelta, uint32_t seed_, "
+                    f"const unsigned bx_, const unsigned by_, const unsigned gdx_, char *zsm_) {{")
         return (f"__global__ void __launch_bounds__({threads}) {name}(char *__restrict__ A, uint32_t sdelta, "
-                f"uint32_t seed_) {{")
+                f"uint32_t seed_) {{\n    const unsigned bx_ = blockIdx.x, by_ = blockIdx.y, gdx_ = gridDim.x; (void)by_; (void)gdx_;")
+
+    @property
+    def member(self) -> bool:
+        return self.k.id in self.gen.member_slot
+
+    def wrapper(self, name) -> str:
+        return (f"__global__ void __launch_bounds__({self.nthreads}) {name}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{\n"
+                f"    __shared__ __align__(16) char zsm_[{max(16, self.zsm_bytes)}];\n"
+                f"    {name}_body(A, sdelta, seed_, blockIdx.x, blockIdx.y, gridDim.x, zsm_);\n}}")
 
     def comment(self, sched) -> str:
         k = self.k
@@ -517,18 +533,25 @@ class KernelGen:
         (stream), `sdelta`, `seed`."""
         choice = self.choose()
         self.strategy = choice[0]
+        self.zsm_bytes = 0
+        self.grid = None
         base = f"k{self.k.id}"
         if choice[0] == "serial":
             return self.gen_serial(base)
-        if choice[0] == "eltwise":
-            return self.gen_eltwise(base, choice[1])
-        if choice[0] == "thread":
-            return self.gen_thread(base)
         if choice[0] == "gemm":
             return self.gen_gemm(base, choice[1])
-        if choice[0] == "coop4":
-            return self.gen_coop_col4(base, *choice[1:])
-        return self.gen_coop(base, *choice[1:])
+        if choice[0] == "eltwise":
+            src, launch = self.gen_eltwise(base, choice[1])
+        elif choice[0] == "thread":
+            src, launch = self.gen_thread(base)
+        elif choice[0] == "coop4":
+            src, launch = self.gen_coop_col4(base, *choice[1:])
+        else:
+            return self.gen_coop(base, *choice[1:])
+        if self.member:
+            assert self.grid is not None
+            src += "\n" + self.wrapper(base)
+        return src, launch
 
     @property
     def side(self) -> bool:
@@ -536,7 +559,15 @@ class KernelGen:
         split reduction go to a scratch region and counters of their own."""
         return self.k.id in self.gen.side_ids
 
+    @property
+    def ticket_base(self) -> int:
+        return self.gen.member_slot.get(self.k.id, (0, 0))[1]
+
     def scratch(self, nbytes: int) -> int:
+        if self.member:                                  # members of one launch keep their partial sums apart
+            off = self.gen.member_slot[self.k.id][0]
+            self.gen.side_scratch_bytes = max(self.gen.side_scratch_bytes, off + nbytes)
+            return self.gen.plan.side_scratch_off + off
         if self.side:
             self.gen.side_scratch_bytes = max(self.gen.side_scratch_bytes, nbytes)
             return self.gen.plan.side_scratch_off
@@ -552,13 +583,14 @@ class KernelGen:
         NT = k.out_numel() // L
         sc = Scope(self, self.names, L, vv)
         sc.statements()
-        body = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {NT}L; tid += (long)gridDim.x * {THREADS}L) {{",
+        body = [f"    for (long tid = bx_ * {THREADS}L + threadIdx.x; tid < {NT}L; tid += (long)gdx_ * {THREADS}L) {{",
                 f"        const {index_t(NT)} u = ({index_t(NT)})tid;"]
         body += self.decode("u", k.domain, self.names, "        ", vv, L)
         body += self.lane_vars(vv, L, "        ") if vv is not None else []
         src = [self.comment(f"elementwise, {L} element(s) per thread"), self.head(base, THREADS)]
         src += self.pointer_decls() + body + sc.lines + ["    }", "}"]
         blocks = max(1, min((NT + THREADS - 1) // THREADS, MAX_BLOCKS))
+        self.grid = (blocks, 1)
         self.notes = f"eltwise x{L}"
         return "\n".join(src), [self.launch_line(base, blocks, THREADS)]
 
@@ -601,12 +633,13 @@ class KernelGen:
         sc = Scope(self, self.names)
         red_lines = self.red_loops_serial(sc, "        ")
         sc.statements()
-        body = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {NT}L; tid += (long)gridDim.x * {THREADS}L) {{",
+        body = [f"    for (long tid = bx_ * {THREADS}L + threadIdx.x; tid < {NT}L; tid += (long)gdx_ * {THREADS}L) {{",
                 f"        const {index_t(NT)} u = ({index_t(NT)})tid;"]
         body += self.decode("u", k.domain, self.names, "        ")
         src = [self.comment("reduction inside the thread"), self.head(base, THREADS)]
         src += self.pointer_decls() + body + red_lines + sc.lines + ["    }", "}"]
         blocks = max(1, min((NT + THREADS - 1) // THREADS, MAX_BLOCKS))
+        self.grid = (blocks, 1)
         self.notes = "thread"
         return "\n".join(src), [self.launch_line(base, blocks, THREADS)]
 
@@ -646,12 +679,12 @@ class KernelGen:
             lines.append(f"{ind}const int ry = threadIdx.x % {RY}, ox = threadIdx.x / {RY};")
         else:
             lines.append(f"{ind}const int ox = threadIdx.x % {OX}, ry = threadIdx.x / {OX};")
-        lines.append(f"{ind}const long o_ = blockIdx.x * {OX}L + ox;")
+        lines.append(f"{ind}const long o_ = bx_ * {OX}L + ox;")
         lines.append(f"{ind}const bool live = o_ < {ON}L;")
         lines.append(f"{ind}const {index_t(ON)} u = ({index_t(ON)})(live ? o_ : {ON - 1}L);")
         lines += self.decode("u", k.domain, self.names, ind)
         lines.append(f"{ind}{T} acc = {OP}::id<{T}>();")
-        lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RNL}L, rbeg + {chunk}L);")
+        lines.append(f"{ind}const long rbeg = by_ * {chunk}L, rend = min({RNL}L, rbeg + {chunk}L);")
         lines.append("#pragma unroll 4")                 # several rows' loads in flight; the adds keep their order
         lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
         inner = ind + "    "
@@ -702,7 +735,7 @@ class KernelGen:
             return "\n".join(src), launch
         # split: partial results to scratch, second kernel combines them in order and runs the statements
         soff = self.scratch(4 * ON * S)
-        lines.append(f"{ind}if (ry == 0 && live) (({T} *)(A + {soff}UL))[blockIdx.y * {ON}L + o_] = acc;")   # [slice][output]
+        lines.append(f"{ind}if (ry == 0 && live) (({T} *)(A + {soff}UL))[by_ * {ON}L + o_] = acc;")   # [slice][output]
         part = [self.comment(f"split reduction, part 1 of 2 ({layout}, {S} CTAs per output group)"),
                 self.head(base + "_part", nthreads)] + self.pointer_decls() + lines + ["}"]
         # final
@@ -710,7 +743,7 @@ class KernelGen:
         self.ptrs = {}
         fsc = Scope(self, self.names, 1, None, "        ")
         fsc.statements()
-        fl = [f"    for (long tid = blockIdx.x * {THREADS}L + threadIdx.x; tid < {ON}L; tid += (long)gridDim.x * {THREADS}L) {{",
+        fl = [f"    for (long tid = bx_ * {THREADS}L + threadIdx.x; tid < {ON}L; tid += (long)gdx_ * {THREADS}L) {{",
               f"        const {index_t(ON)} u = ({index_t(ON)})tid;"]
         fl += self.decode("u", k.domain, self.names, "        ")
         fl.append(f"        {T} acc = {OP}::id<{T}>();")
@@ -739,12 +772,12 @@ class KernelGen:
         chunk = (RN + S - 1) // S
         ind = "    "
         lines = [f"{ind}const int ox = threadIdx.x % {OX}, ry = threadIdx.x / {OX};",
-                 f"{ind}const long o_ = blockIdx.x * {OX}L + ox;",
+                 f"{ind}const long o_ = bx_ * {OX}L + ox;",
                  f"{ind}const bool live = o_ < {OG}L;",
                  f"{ind}const {index_t(OG)} u = ({index_t(OG)})(live ? o_ : {OG - 1}L);"]
         lines += self.decode("u", k.domain, self.names, ind, vv, 4) + self.lane_vars(vv, 4, ind)
         lines.append(f"{ind}float acc_0 = {OP}::id<float>(), acc_1 = acc_0, acc_2 = acc_0, acc_3 = acc_0;")
-        lines.append(f"{ind}const long rbeg = blockIdx.y * {chunk}L, rend = min({RN}L, rbeg + {chunk}L);")
+        lines.append(f"{ind}const long rbeg = by_ * {chunk}L, rend = min({RN}L, rbeg + {chunk}L);")
         lines.append("#pragma unroll 8")                 # several rows' loads in flight; the adds keep their order
         lines.append(f"{ind}for (long rr_ = rbeg + ry; rr_ < rend; rr_ += {RY}) {{")
         inner = ind + "    "
@@ -757,7 +790,12 @@ class KernelGen:
         for i, v in enumerate(vals):
             lines.append(f"{inner}acc_{i} = {OP}::f(acc_{i}, {v});")
         lines.append(f"{ind}}}")
-        lines.append(f"{ind}__shared__ float sm_[{RY}][{4 * OX + 4}];")
+        W = 4 * OX + 4
+        self.zsm_bytes = RY * W * 4 + 16
+        if self.member:                                  # shared memory comes from the launch this kernel is a member of
+            lines.append(f"{ind}float (*sm_)[{W}] = reinterpret_cast<float (*)[{W}]>(zsm_);")
+        else:
+            lines.append(f"{ind}__shared__ float sm_[{RY}][{W}];")
         for i in range(4):
             lines.append(f"{ind}sm_[ry][4 * ox + {i}] = acc_{i};")
         lines.append(f"{ind}__syncthreads();")
@@ -781,6 +819,7 @@ class KernelGen:
             src = [self.comment(f"cooperative reduction (col, {OX} x 4 outputs x {RY} threads)"),
                    self.head(base, nthreads)] + self.pointer_decls() + lines + ["}"]
             launch.append(self.launch_line(base, f"dim3({gx}, 1)", nthreads))
+            self.grid = (gx, 1)
             self.notes = f"coop col4 {OX}x{RY}"
             return "\n".join(src), launch
         # Split over S CTAs per output group, finished by whichever of them arrives last: every CTA writes its partial
@@ -802,9 +841,11 @@ class KernelGen:
         for i in range(4):
             tree.append(f"{ind}acc_{i} = sm_[0][4 * ox + {i}];")
         lines.append(f"{ind}float *part_ = (float *)(A + {soff}UL);")
-        lines.append(f"{ind}if (ry == 0 && live) *reinterpret_cast<float4 *>(part_ + blockIdx.y * {ON}L + o_ * 4) = make_float4(acc_0, acc_1, acc_2, acc_3);")
-        lines += [f"{ind}__threadfence();", f"{ind}__shared__ unsigned last_;", f"{ind}__syncthreads();",
-                  f"{ind}unsigned *ticket_ = (unsigned *)(A + {'ANVIL_RT_SIDE_TICKETS_OFF' if self.side else 'ANVIL_RT_TICKETS_OFF'}) + blockIdx.x;",
+        lines.append(f"{ind}if (ry == 0 && live) *reinterpret_cast<float4 *>(part_ + by_ * {ON}L + o_ * 4) = make_float4(acc_0, acc_1, acc_2, acc_3);")
+        last_decl = (f"{ind}unsigned &last_ = *reinterpret_cast<unsigned *>(zsm_ + {RY * W * 4});" if self.member
+                     else f"{ind}__shared__ unsigned last_;")
+        lines += [f"{ind}__threadfence();", last_decl, f"{ind}__syncthreads();",
+                  f"{ind}unsigned *ticket_ = (unsigned *)(A + {'ANVIL_RT_SIDE_TICKETS_OFF' if self.side else 'ANVIL_RT_TICKETS_OFF'}) + {self.ticket_base}u + bx_;",
                   f"{ind}if (threadIdx.x == 0) last_ = atomicAdd(ticket_, 1u) == {S - 1}u;",
                   f"{ind}__syncthreads();", f"{ind}if (!last_) return;", f"{ind}__threadfence();"]
         for i in range(4):
@@ -829,6 +870,7 @@ class KernelGen:
         src = [self.comment(f"split reduction finished by the last CTA (col, 4 outputs per thread, {S} CTAs per output group)"),
                self.head(base, nthreads)] + self.pointer_decls() + lines + ["}"]
         launch.append(self.launch_line(base, f"dim3({gx}, {S})", nthreads))
+        self.grid = (gx, S)
         self.notes = f"split col4 {OX}x{RY} S{S}"
         return "\n".join(src), launch
 
@@ -1118,6 +1160,11 @@ class KernelGen:
 def os_environ(name: str, default: str) -> str:
     import os
     return os.environ.get(name, default)
+
+
+def use_zgroups() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_ZGROUPS", "1") != "0"
 
 
 def use_side_stream() -> bool:
@@ -1613,6 +1660,8 @@ class ProgramGen:
         self.side_scratch_bytes = 4
         self.deferred = an.deferred_kernels(prog) if use_side_stream() else set()
         self.side_ids: set = set()                   # deferred kernels that are launch units of their own: they run on the second stream
+        self.member_slot: dict = {}                  # kernel id -> (scratch offset, first ticket) inside its side-by-side launch
+        self.zgroup_of: dict = {}                    # kernel id -> ids of the side-by-side launch it belongs to
         self.readers: dict = {}
         for k in prog.kernels():
             for r in k.reads():
@@ -1622,6 +1671,7 @@ class ProgramGen:
         self.kernel_index: dict[int, int] = {}
         self.kernels: list[kir.Kernel] = []
         self.kernel_src: list[str] = []
+        self.kernel_gens: dict = {}
         self.launchers: list[str] = []
         self.kernel_notes: list[str] = []
         self.tables: list[str] = []
@@ -1740,6 +1790,84 @@ class ProgramGen:
                                     + "\n".join(body) + "\n}")
         return idx
 
+    ZGROUP_MAX = 8
+
+    def plan_zgroups(self, side_kernels: list) -> None:
+        """Side-stream kernels of one launch run become side-by-side launches of up to ZGROUP_MAX members: they are
+        independent of everything after them (that is what put them on the second stream), so also of one another, and
+        each is too short to fill the GPU or to hide its own latency chain (C5: a 16384 x 512 column sum with its Adam
+        update is 16 us for 33 MB). A member must be generated as a device function, so only kernels without source yet
+        are taken, and only the strategies whose bodies are written against bx_ / by_ / gdx_."""
+        cur: list = []
+
+        def flush():
+            if len(cur) >= 2:
+                ids = tuple(k.id for k, _, _ in cur)
+                soff = tick = 0
+                for k, nbytes, gx in cur:
+                    self.member_slot[k.id] = (soff, tick)
+                    self.zgroup_of[k.id] = ids
+                    soff += (nbytes + 255) // 256 * 256
+                    tick += gx
+            cur.clear()
+        for k in side_kernels:
+            if k.id in self.kernel_index or k.id in self.zgroup_of:
+                flush()
+                continue
+            choice = KernelGen(self, k).choose()
+            if choice[0] == "coop4":
+                OX, RY, S = choice[1:]
+                gx = (k.out_numel() // 4 + OX - 1) // OX
+                need = (4 * k.out_numel() * S if S > 1 else 0, gx if S > 1 else 0)
+                ok = OX * RY == THREADS
+            elif choice[0] in ("eltwise", "thread"):
+                need, ok = (0, 0), True
+            else:
+                ok = False
+            if not ok:
+                flush()
+                continue
+            if len(cur) == self.ZGROUP_MAX or sum(g for _, _, g in cur) + need[1] > 256:
+                flush()
+            cur.append((k, need[0], need[1]))
+        flush()
+
+    def add_zgroup(self, kernels: list) -> int:
+        """Launch-table index of the side-by-side launch of these (mutually independent) kernels."""
+        key = ("z",) + tuple(k.id for k in kernels)
+        hit = self.groups.get(key)
+        if hit is not None:
+            return hit
+        idx = len(self.groups)
+        name = f"z{idx}_{kernels[0].id}"
+        gens = []
+        for k in kernels:
+            kg = self.kernel_gens[k.id]
+            assert kg.member and kg.grid is not None and kg.nthreads == THREADS
+            gens.append(kg)
+        smem = max(16, max(kg.zsm_bytes for kg in gens))
+        lines = [f"// side by side: {' | '.join(k.name for k in kernels)}",
+                 f"__global__ void __launch_bounds__({THREADS}) {name}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
+                 f"    __shared__ __align__(16) char zsm_[{smem}];", "    const unsigned b_ = blockIdx.x;"]
+        off = 0
+        for k, kg in zip(kernels, gens):
+            gx, gy = kg.grid
+            lines.append(f"    if (b_ < {off + gx * gy}u) {{ const unsigned l_ = b_ - {off}u; "
+                         f"k{k.id}_body(A, 0u, seed_, l_ % {gx}u, l_ / {gx}u, {gx}u, zsm_); return; }}")
+            off += gx * gy
+        lines.append("}")
+        self.groups[key] = idx
+        self.group_src.append("\n".join(lines))
+        self.group_notes.append(f"zgroup x{len(kernels)} " + "+".join(sorted({" ".join(kg.notes.split()[:2]) for kg in gens})))
+        body = ["    char *A = (char *)anvil_rt_ptr(rt, 0);", "    cudaStream_t st = (cudaStream_t)anvil_rt_stream(rt);",
+                "    uint32_t seed = anvil_rt_get_seed(rt);",
+                f"    RT(anvil_rt_prof_begin(rt, PROF_GROUP0 + {idx}));",
+                f"    {name}<<<{off}, {THREADS}, 0, st>>>(A, 0u, seed); anvil_rt_count_launches(rt, 1);",
+                f"    RT(anvil_rt_prof_end(rt, PROF_GROUP0 + {idx}));"] + self.check_lines(kernels) + ["    return 0;"]
+        self.group_launchers.append(f"static int launch_group_{idx}(anvil_rt *rt) {{   // {' | '.join(k.name for k in kernels)}\n"
+                                    + "\n".join(body) + "\n}")
+        return idx
+
     MAX_FAULT_CODES = 254
 
     def add_attention(self, g) -> int:
@@ -1808,6 +1936,7 @@ class ProgramGen:
             return hit
         kg = KernelGen(self, k)
         src, launch = kg.generate()
+        self.kernel_gens[k.id] = kg
         idx = len(self.kernels)
         self.kernel_index[k.id] = idx
         self.kernels.append(k)
@@ -1881,6 +2010,8 @@ class ProgramGen:
                             if kq.id in self.deferred and kq.id not in self.kernel_index and ct.match(kq) is None:
                                 self.side_ids.add(kq.id)
                             q += 1
+                if in_loop and use_zgroups():
+                    self.plan_zgroups([kq for kq in run_kernels if kq.id in self.side_ids])
                 for x in stmts[i:j]:
                     kj = x.kernel
                     self.add_kernel(kj)
@@ -1914,13 +2045,25 @@ class ProgramGen:
                     else:
                         idx = self.kernel_index[run_kernels[q].id]
                         run.append(idx)
-                        if run_kernels[q].id in self.side_ids:
+                        zg = self.zgroup_of.get(run_kernels[q].id)
+                        if zg is not None:               # runs when the last member of its side-by-side launch is reached
+                            if run_kernels[q].id == zg[-1]:
+                                by_id = {x.id: x for x in run_kernels}
+                                ks = [by_id[i_] for i_ in zg]
+                                gi = self.add_zgroup(ks)
+                                calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);")
+                                forked = True
+                                if self.record_units:
+                                    self.hot_units.append((("g", gi), self.group_notes[gi], ks))
+                        elif run_kernels[q].id in self.side_ids:
                             calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_{idx}(rt)); anvil_rt_back(rt);")
                             forked = True
+                            if self.record_units:
+                                self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
                         else:
                             calls.append(f"RT(launch_{idx}(rt));")
-                        if self.record_units:
-                            self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
+                            if self.record_units:
+                                self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
                         q += 1
                 if forked:
                     calls.append("RT(anvil_rt_join(rt));")

@@ -50,7 +50,30 @@ def test_every_fork_is_joined_inside_its_graph(monkeypatch):
     side_split = [i for i in g.side_ids if g.kernel_notes[g.kernel_index[i]].startswith("split col4")]
     assert side_split and g.plan.side_scratch_bytes >= 4 * 512 * 128
     body = g.kernel_src[g.kernel_index[side_split[0]]]
-    assert "ANVIL_RT_SIDE_TICKETS_OFF" in body and f"A + {g.plan.side_scratch_off}UL" in body
+    first_off = g.member_slot.get(side_split[0], (0, 0))[0]
+    assert "ANVIL_RT_SIDE_TICKETS_OFF" in body and f"A + {g.plan.side_scratch_off + first_off}UL" in body
+    # ... and from one another when several of them share a launch: disjoint scratch ranges and ticket ranges
+    groups = {}
+    for i in side_split:
+        if i in g.zgroup_of:
+            groups.setdefault(g.zgroup_of[i], []).append(i)
+    assert groups
+    for ids, members in groups.items():
+        spans = []
+        ticks = []
+        for i in members:
+            kg = g.kernel_gens[i]
+            soff, tick = g.member_slot[i]
+            gx, S = kg.grid
+            spans.append((soff, soff + 4 * kg.k.out_numel() * S))
+            ticks.append((tick, tick + gx))
+        for rng in (sorted(spans), sorted(ticks)):
+            assert all(a[1] <= b[0] for a, b in zip(rng, rng[1:]))
+        assert max(t[1] for t in ticks) <= 256 and max(sp[1] for sp in spans) <= g.plan.side_scratch_bytes
+        assert len(ids) <= g.ZGROUP_MAX
+    # a side-by-side launch appears once, at its last member, between a fork and the join
+    z = re.findall(r"launch_group_(\d+)\(rt\)\); anvil_rt_back", src)
+    assert len(set(z)) == len([n for n in g.group_notes if n.startswith("zgroup")])
     monkeypatch.setenv("ANVIL_B200_SIDE", "0")
     src0, g0 = emit.generate(load("c5_transformer"), seed=0)
     assert "anvil_rt_fork" not in src0 and not g0.side_ids
