@@ -566,8 +566,11 @@ class KernelGen:
     def scratch(self, nbytes: int) -> int:
         if self.member:                                  # members of one launch keep their partial sums apart
             off = self.gen.member_slot[self.k.id][0]
-            self.gen.side_scratch_bytes = max(self.gen.side_scratch_bytes, off + nbytes)
-            return self.gen.plan.side_scratch_off + off
+            if self.side:
+                self.gen.side_scratch_bytes = max(self.gen.side_scratch_bytes, off + nbytes)
+                return self.gen.plan.side_scratch_off + off
+            self.gen.need_scratch(off + nbytes)
+            return self.gen.plan.scratch_off + off
         if self.side:
             self.gen.side_scratch_bytes = max(self.gen.side_scratch_bytes, nbytes)
             return self.gen.plan.side_scratch_off
@@ -1792,12 +1795,16 @@ class ProgramGen:
 
     ZGROUP_MAX = 8
 
-    def plan_zgroups(self, side_kernels: list) -> None:
+    def plan_zgroups(self, side_kernels: list, neighbours: bool = False) -> None:
         """Side-stream kernels of one launch run become side-by-side launches of up to ZGROUP_MAX members: they are
         independent of everything after them (that is what put them on the second stream), so also of one another, and
         each is too short to fill the GPU or to hide its own latency chain (C5: a 16384 x 512 column sum with its Adam
         update is 16 us for 33 MB). A member must be generated as a device function, so only kernels without source yet
-        are taken, and only the strategies whose bodies are written against bx_ / by_ / gdx_."""
+        are taken, and only the strategies whose bodies are written against bx_ / by_ / gdx_.
+        `neighbours`: the list is a launch run of the first stream (None = something that cannot join); consecutive
+        kernels join when none of them reads or writes what another writes (the bias-gradient sums of a data-parallel
+        step, which go to the all-reduce bucket and so are not deferred) and none writes a tensor that shares arena
+        bytes (lifetime sharing relies on the program's order between launches)."""
         cur: list = []
 
         def flush():
@@ -1811,9 +1818,19 @@ class ProgramGen:
                     tick += gx
             cur.clear()
         for k in side_kernels:
-            if k.id in self.kernel_index or k.id in self.zgroup_of:
+            if k is None or k.id in self.kernel_index or k.id in self.zgroup_of or (neighbours and (k.id in self.side_ids or k.uses_rand())):
                 flush()
                 continue
+            if neighbours:
+                r, w = {b.id for b in k.reads()}, {b.id for b in k.writes()}
+                if w & self.plan.shared:                 # its output may live in bytes another member still reads: the
+                    flush()                              # arena plan assumes the program's order between launches
+                    continue
+                for m, _, _ in cur:
+                    mr, mw = {b.id for b in m.reads()}, {b.id for b in m.writes()}
+                    if w & (mr | mw) or r & mw:
+                        flush()
+                        break
             choice = KernelGen(self, k).choose()
             if choice[0] == "coop4":
                 OX, RY, S = choice[1:]
@@ -2012,6 +2029,21 @@ class ProgramGen:
                             q += 1
                 if in_loop and use_zgroups():
                     self.plan_zgroups([kq for kq in run_kernels if kq.id in self.side_ids])
+                    # first-stream kernels: only neighbours that do not touch one another's results
+                    q, singles = 0, []
+                    while q < len(run_kernels):
+                        if q in astarts:
+                            q = astarts[q][0]
+                        elif q in hstarts:
+                            q = hstarts[q][0]
+                        elif q in starts:
+                            q = starts[q]
+                        else:
+                            singles.append(run_kernels[q])
+                            q += 1
+                            continue
+                        singles.append(None)             # a fused launch stands between
+                    self.plan_zgroups(singles, neighbours=True)
                 for x in stmts[i:j]:
                     kj = x.kernel
                     self.add_kernel(kj)
@@ -2046,13 +2078,18 @@ class ProgramGen:
                         idx = self.kernel_index[run_kernels[q].id]
                         run.append(idx)
                         zg = self.zgroup_of.get(run_kernels[q].id)
+                        by_id = {x.id: x for x in run_kernels}
+                        if zg is not None and not all(i_ in by_id for i_ in zg):
+                            zg = None                    # a member is fed from the host in this variant of the loop body: no shared launch
                         if zg is not None:               # runs when the last member of its side-by-side launch is reached
                             if run_kernels[q].id == zg[-1]:
-                                by_id = {x.id: x for x in run_kernels}
                                 ks = [by_id[i_] for i_ in zg]
                                 gi = self.add_zgroup(ks)
-                                calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);")
-                                forked = True
+                                if zg[0] in self.side_ids:
+                                    calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);")
+                                    forked = True
+                                else:
+                                    calls.append(f"RT(launch_group_{gi}(rt));")
                                 if self.record_units:
                                     self.hot_units.append((("g", gi), self.group_notes[gi], ks))
                         elif run_kernels[q].id in self.side_ids:

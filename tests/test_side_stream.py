@@ -91,3 +91,26 @@ def test_what_a_deferred_kernel_reads_lives_until_the_join():
                 assert uses[r.id][-1].pos >= uses0[r.id][-1].pos
                 longer += uses[r.id][-1].pos > uses0[r.id][-1].pos
     assert longer > 0
+
+
+def test_first_stream_groups_write_no_tensor_that_shares_bytes():
+    """Kernels of one launch run concurrently, but lifetime sharing of arena bytes relies on the program's order: a
+    first-stream member may therefore not write a tensor whose bytes another tensor had before."""
+    from anvil_lang_b200 import dp
+    from util import GOLDEN
+    progs = [kir.load(os.path.join(GOLDEN, "transformer_small.kir.json.gz")), dp.shard(load("c5_transformer.b8"), 8)]
+    seen = 0
+    for prog in progs:
+        src, g = emit.generate(prog, seed=0)
+        assert g.plan.shared
+        for kid, ids in g.zgroup_of.items():
+            if ids[0] in g.side_ids:
+                continue
+            seen += 1
+            k = g.kernels[g.kernel_index[kid]]
+            assert not ({b.id for b in k.writes()} & g.plan.shared)
+            for other in ids:                                   # and the members do not touch one another's results
+                if other != kid:
+                    o = g.kernels[g.kernel_index[other]]
+                    assert not ({b.id for b in k.writes()} & ({b.id for b in o.reads()} | {b.id for b in o.writes()}))
+    assert seen > 0
