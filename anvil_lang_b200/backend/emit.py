@@ -937,9 +937,12 @@ class KernelGen:
                 if not (any(v in vs for v in c.mvars) and any(v in vs for v in c.nvars)):
                     continue                                 # a bias row or a per-row scalar: cached anyway
                 seen.add((buf.root.id, off.key()))
-                sc.emit(f"anvil::prefetch_l2({self.ptr(buf, False)} + ({sc.affine(off, 0)}));")
+                sc.emit(f"anvil::{self.prefetch}({self.ptr(buf, False)} + ({sc.affine(off, 0)}));")
             return None
+        self.prefetch = "prefetch_l2"
         fe = fe + self.functor_method("void epi_touch(int m, int n, int bt)", dm + dn + db, touch)
+        self.prefetch = "prefetch_l1"                        # the same lines into L1, right before the epilogue reads them
+        fe = fe + self.functor_method("void epi_near(int m, int n, int bt)", dm + dn + db, touch)
 
         # Two-phase form of the statements: epi_loads fetches what they read at (m, n) — tensors this kernel
         # never writes, and the old value of an exclusive `+=` — and epi2 runs them on those values, so a
@@ -1605,6 +1608,7 @@ class HGroupGen:
             f += dispatch("void b_touch(int k, int n, int bt)", "b_touch(k, {v}, bt)", sizes, "n")
             f += dispatch("void epi(int m, int n, int bt, float acc)", "epi(m, {v}, bt, acc)", sizes, "n")
             f += dispatch("void epi_touch(int m, int n, int bt)", "epi_touch(m, {v}, bt)", sizes, "n")
+            f += dispatch("void epi_near(int m, int n, int bt)", "epi_near(m, {v}, bt)", sizes, "n")
             f += dispatch(f"void epi_loads(int m, int n, int bt, float (&ld)[{L}])",
                           "epi_loads(m, {v}, bt, reinterpret_cast<float (&)[{L}]>(ld))", sizes, "n")
             f += dispatch(f"void epi2(int m, int n, int bt, float acc, const float (&ld)[{L}])",
@@ -1617,6 +1621,7 @@ class HGroupGen:
             f += dispatch("void b_touch(int k, int n, int bt)", "b_touch({v}, n, bt)", sizes, "k")
             f += [f"    __device__ __forceinline__ void epi(int m, int n, int bt, float acc) const {{ {first}{{A}}.epi(m, n, bt, acc); }}",
                   f"    __device__ __forceinline__ void epi_touch(int m, int n, int bt) const {{ {first}{{A}}.epi_touch(m, n, bt); }}",
+                  f"    __device__ __forceinline__ void epi_near(int m, int n, int bt) const {{ {first}{{A}}.epi_near(m, n, bt); }}",
                   f"    __device__ __forceinline__ void epi_loads(int m, int n, int bt, float (&ld)[{L}]) const {{ {first}{{A}}.epi_loads(m, n, bt, ld); }}",
                   f"    __device__ __forceinline__ void epi2(int m, int n, int bt, float acc, const float (&ld)[{L}]) const {{ {first}{{A}}.epi2(m, n, bt, acc, ld); }}"]
         f.append("};")

@@ -135,6 +135,7 @@ ANVIL_DEV Arg<T> warp_arg_reduce(Arg<T> a) {
 
 // Asks for the line holding *p to be brought into L2; never faults, returns nothing.
 ANVIL_DEV void prefetch_l2(const void *p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+ANVIL_DEV void prefetch_l1(const void *p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 
 // ---------------------------------------------------------------------------- 128-bit access
 ANVIL_DEV float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }

@@ -997,6 +997,10 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
     // statements read, then the statements. release >= 0: hand tensor-memory buffer `release` back after the loads.
     auto drain = [&](const Item &it, uint32_t acc, int c, float *stage_f, int release, uint32_t tempty_leader0) {
         const int q = warp & 3;
+        // What the statements read at this piece (32 rows of one 128-byte line each) is asked into L1 first: the loads
+        // below go out eight rows at a time, and every batch that has to go to L2 costs its full latency — with long k
+        // loops (two accumulators, no second tensor-memory buffer) nothing hides the epilogue.
+        if (SPLIT == 1 && F::NLD > 0 && it.m0 + 32 * q + lane < M && it.n0 + 32 * c < N) f.epi_near(it.m0 + 32 * q + lane, it.n0 + 32 * c, it.bt);
         uint32_t r[32];
         tmem_ld32(acc + (uint32_t)(32 * c), r);
         if (ACCS == 2) {
@@ -1014,7 +1018,7 @@ __device__ __forceinline__ void gemm_tc_pair_persistent(const F &f, float *__res
         for (int x = 0; x < 32; x++) stage_f[lane * 33 + x] = __uint_as_float(r[x]);
         __syncwarp();
         const int n = it.n0 + 32 * c + lane;
-        constexpr int RB = 8, NLD = F::NLD > 0 ? F::NLD : 1;
+        constexpr int NLD = F::NLD > 0 ? F::NLD : 1, RB = 8;
         for (int r0 = 0; r0 < 32; r0 += RB) {
             const int mb = it.m0 + 32 * q + r0;
             float ld[RB][NLD];
