@@ -1624,6 +1624,51 @@ class HGroupGen:
                   f"    __device__ __forceinline__ void epi_near(int m, int n, int bt) const {{ {first}{{A}}.epi_near(m, n, bt); }}",
                   f"    __device__ __forceinline__ void epi_loads(int m, int n, int bt, float (&ld)[{L}]) const {{ {first}{{A}}.epi_loads(m, n, bt, ld); }}",
                   f"    __device__ __forceinline__ void epi2(int m, int n, int bt, float acc, const float (&ld)[{L}]) const {{ {first}{{A}}.epi2(m, n, bt, acc, ld); }}"]
+        # The same methods as templates on the member index: the resident template looks the member of a whole k block
+        # (kcat) or tile (ncat) up once and instantiates its loops per member (no branch inside an operand fetch).
+        if len(names) <= 4:
+            sizes = [c.N for c in cs] if kind == "ncat" else [c.K for c in cs]
+            bases = [sum(sizes[:i]) for i in range(len(sizes))]
+
+            def chain(var):
+                out = "0"
+                for i in range(1, len(sizes)):
+                    out = f"({var} >= {bases[i]} ? {i} : {out})"
+                return out
+
+            def per_member(sig, call, own, shift):
+                """own: every member has the method (else the first member's is used); shift: which argument is rebased."""
+                out = [f"    template <int S> __device__ __forceinline__ {sig} const {{"]
+                for i, fn in enumerate(names):
+                    target = fn if own else first
+                    args = call.format(v=(f"{shift} - {bases[i]}" if (own and bases[i]) else shift), L=max(nlds[i] if own else nlds[0], 1))
+                    out.append(f"        {'if' if i == 0 else 'else if'} constexpr (S == {i}) {{ {target}{{A}}.{args}; }}")
+                return out + ["    }"]
+            f.append(f"    static constexpr int SEGS = {len(names)};")
+            if kind == "ncat":
+                f += [f"    __device__ __forceinline__ int op_seg(int k0, int n0) const {{ return {chain('n0')}; }}",
+                      f"    __device__ __forceinline__ int epi_seg(int n0) const {{ return {chain('n0')}; }}"]
+                f += per_member("void a4s(int m, int k, int bt, float (&v)[4])", "a4(m, k, bt, v)", False, "k")
+                f += per_member("void a_touchs(int m, int k, int bt)", "a_touch(m, k, bt)", False, "k")
+                f += per_member("void b4s(int k, int n, int bt, float (&v)[4])", "b4(k, {v}, bt, v)", True, "n")
+                f += per_member("void b_touchs(int k, int n, int bt)", "b_touch(k, {v}, bt)", True, "n")
+                f += per_member("void epi_touchs(int m, int n, int bt)", "epi_touch(m, {v}, bt)", True, "n")
+                f += per_member("void epi_nears(int m, int n, int bt)", "epi_near(m, {v}, bt)", True, "n")
+                f += per_member(f"void epi_loadss(int m, int n, int bt, float (&ld)[{L}])",
+                                "epi_loads(m, {v}, bt, reinterpret_cast<float (&)[{L}]>(ld))", True, "n")
+                f += per_member(f"void epi2s(int m, int n, int bt, float acc, const float (&ld)[{L}])",
+                                "epi2(m, {v}, bt, acc, reinterpret_cast<const float (&)[{L}]>(ld))", True, "n")
+            else:
+                f += [f"    __device__ __forceinline__ int op_seg(int k0, int n0) const {{ return {chain('k0')}; }}",
+                      "    __device__ __forceinline__ int epi_seg(int n0) const { return 0; }"]
+                f += per_member("void a4s(int m, int k, int bt, float (&v)[4])", "a4(m, {v}, bt, v)", True, "k")
+                f += per_member("void a_touchs(int m, int k, int bt)", "a_touch(m, {v}, bt)", True, "k")
+                f += per_member("void b4s(int k, int n, int bt, float (&v)[4])", "b4({v}, n, bt, v)", True, "k")
+                f += per_member("void b_touchs(int k, int n, int bt)", "b_touch({v}, n, bt)", True, "k")
+                f += per_member("void epi_touchs(int m, int n, int bt)", "epi_touch(m, n, bt)", False, "n")
+                f += per_member("void epi_nears(int m, int n, int bt)", "epi_near(m, n, bt)", False, "n")
+                f += per_member(f"void epi_loadss(int m, int n, int bt, float (&ld)[{L}])", "epi_loads(m, n, bt, ld)", False, "n")
+                f += per_member(f"void epi2s(int m, int n, int bt, float acc, const float (&ld)[{L}])", "epi2(m, n, bt, acc, ld)", False, "n")
         f.append("};")
         seg_bn = 256 if kind != "ncat" or all(c.N % 256 == 0 for c in cs) else 128      # a tile never straddles two members
         BN, S, accs, work = pp_launch_params(M, N, K, 1, seg_bn)
