@@ -165,9 +165,6 @@ class ArenaPlan:
         return self.shared | self.unused
 
 
-SIDE_MAX_FLOPS = 4_000_000_000           # larger kernels (the contractions) stay on the main stream
-
-
 def _stmt_roots(st) -> tuple[set, set]:
     """(root ids read, root ids written) by a statement and everything nested in it; a runtime call or a collective
     counts as reading and writing every tensor it names."""
@@ -211,7 +208,7 @@ def deferred_kernels(prog: kir.Program) -> set:
     reads nor writes what they write, and does not write what they read. They are the updates of biases, gains and
     their optimizer state at the end of a training step. Such a kernel may run on a second stream beside the kernels
     that follow it, as long as it has finished when the list ends. Kernels that draw random numbers (their stream
-    position is ordered) and large ones (contractions want the whole GPU) are left out."""
+    position is ordered) are left out."""
     out: set = set()
 
     def visit(block: kir.Block, in_loop: bool):
@@ -223,7 +220,7 @@ def deferred_kernels(prog: kir.Program) -> set:
                 r, w = _stmt_roots(st)
                 if isinstance(st, kir.KernelStmt):
                     k = st.kernel
-                    if (not k.uses_rand() and k.rand_base is None and kernel_flops(k) <= SIDE_MAX_FLOPS
+                    if (not k.uses_rand() and k.rand_base is None
                             and not (w & (later_r | later_w)) and not (r & later_w)):
                         out.add(k.id)
                 later_r |= r

@@ -1003,8 +1003,7 @@ class KernelGen:
                     f"    anvil::gemm_simt_tile<{fn}, {AK}, {BNC}, 1>({fn}{{A}}, nullptr);", "}"]
             launch.append(self.launch_line(base, f"dim3({tiles}, {NB})", 256))
         else:
-            self.gen.need_scratch(4 * M * N * NB * S)
-            soff = self.gen.plan.scratch_off
+            soff = self.scratch(4 * M * N * NB * S)
             src += [f"__global__ void __launch_bounds__(256) {base}_part(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_simt_tile<{fn}, {AK}, {BNC}, {S}>({fn}{{A}}, (float *)(A + {soff}UL));", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
@@ -1142,14 +1141,13 @@ class KernelGen:
                     f"    {tile_fn}1{tile_tail}({fn}{{A}}, nullptr, {status});", "}"]
         else:
             kname = base + "_part"
-            self.gen.need_scratch(4 * M * N * NB * S)
-            soff = self.gen.plan.scratch_off
+            soff = self.scratch(4 * M * N * NB * S)
             src += [f"__global__ void {attrs}__launch_bounds__({threads}, {per_sm}) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    {tile_fn}{S}{tile_tail}({fn}{{A}}, (float *)(A + {soff}UL), {status});", "}",
                     f"__global__ void __launch_bounds__(256) {base}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
                     f"    anvil::gemm_split_finish<{fn}, {S}>({fn}{{A}}, (const float *)(A + {soff}UL));", "}"]
         tma = pp and use_tma() and tma_kernel(self.gen, src, launch, kname, fn, c, c, AK, BKC, S, accs, BN, status,
-                                              f"(float *)(A + {self.gen.plan.scratch_off}UL)" if S > 1 else "nullptr",
+                                              f"(float *)(A + {soff}UL)" if S > 1 else "nullptr",
                                               f"dim3({grid_x}, {grid_y})", smem)
         if not tma:
             launch.append(f"{{ static bool attr_ = false; if (!attr_) {{ cudaFuncSetAttribute({kname}, "
@@ -1166,6 +1164,11 @@ class KernelGen:
 def os_environ(name: str, default: str) -> str:
     import os
     return os.environ.get(name, default)
+
+
+def use_side_gemms() -> bool:
+    import os
+    return os.environ.get("ANVIL_B200_SIDE_GEMMS", "1") != "0"
 
 
 def use_zgroups() -> bool:
@@ -1678,9 +1681,15 @@ class HGroupGen:
         kname = kernel_name + ("_part" if S > 1 else "")
         smem = f"anvil::tc::pp_smem_bytes({BN})"
         scratch = "nullptr"
+        soff = 0
         if S > 1:
-            gen.need_scratch(4 * M * N * S)
-            scratch = f"(float *)(A + {gen.plan.scratch_off}UL)"
+            if all(k.id in gen.side_ids for k in ks):        # runs on the second stream, beside first-stream products
+                gen.side_scratch_bytes = max(gen.side_scratch_bytes, 4 * M * N * S)
+                soff = gen.plan.side_scratch_off
+            else:
+                gen.need_scratch(4 * M * N * S)
+                soff = gen.plan.scratch_off
+            scratch = f"(float *)(A + {soff}UL)"
         f += [f"__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(anvil::tc::PP_THREADS, 1) {kname}(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
               f"    anvil::tc::gemm_tc_pair_persistent<{name}, {AK}, {BKC}, {S}, {accs}, {BN}>({name}{{A}}, {scratch}, {status});", "}"]
         launch = []
@@ -1691,7 +1700,7 @@ class HGroupGen:
                       f"{kname}<<<dim3({2 * min(work, 74)}, 1), anvil::tc::PP_THREADS, {smem}, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);"]
         if S > 1:
             f += [f"__global__ void __launch_bounds__(256) {kernel_name}_fin(char *__restrict__ A, uint32_t sdelta, uint32_t seed_) {{",
-                  f"    anvil::gemm_split_finish<{name}, {S}>({name}{{A}}, (const float *)(A + {gen.plan.scratch_off}UL));", "}"]
+                  f"    anvil::gemm_split_finish<{name}, {S}>({name}{{A}}, (const float *)(A + {soff}UL));", "}"]
             fb_ = max(1, min((M * N + 255) // 256, MAX_BLOCKS))
             launch.append(f"{kernel_name}_fin<<<{fb_}, 256, 0, st>>>(A, sdelta, seed); anvil_rt_count_launches(rt, 1);")
         note = f"gemm tc 1x{M}x{N}x{K} S{S} pp {kind}{len(ks)}"
@@ -1713,6 +1722,7 @@ class ProgramGen:
         self.side_scratch_bytes = 4
         self.deferred = an.deferred_kernels(prog) if use_side_stream() else set()
         self.side_ids: set = set()                   # deferred kernels that are launch units of their own: they run on the second stream
+        self.dealt = [0, 0]                          # FLOPs of deferred contractions given to the first / second stream so far
         self.member_slot: dict = {}                  # kernel id -> (scratch offset, first ticket) inside its side-by-side launch
         self.zgroup_of: dict = {}                    # kernel id -> ids of the side-by-side launch it belongs to
         self.readers: dict = {}
@@ -2063,22 +2073,38 @@ class ProgramGen:
                 hstarts = {a: (b, kind) for a, b, kind in (hfuse.find_hgroups(run_kernels, tc_eligible_pp) if use_hgroups() else [])}
                 astarts = {a: (b, g) for a, b, g in (at.find_attention(run_kernels, self.readers, self.host_read, self.causal_e)
                                                        if use_attention() else [])}
-                if in_loop:                          # deferred kernels that stay launch units of their own go to the second stream
+                if in_loop:
+                    # Deferred kernels that stay launch units of their own go to the second stream (decided once, before
+                    # the kernel's source exists). Deferred contractions (the weight gradients with their updates, at the
+                    # end of a training step) are dealt to the two streams by accumulated work: two chains of resident
+                    # kernels fill each other's partly empty last round of tiles.
+                    def deal(ks_):
+                        if not use_side_gemms() or any(x.id not in self.deferred or x.id in self.kernel_index for x in ks_):
+                            return
+                        fl = sum(an.kernel_flops(x) for x in ks_)
+                        if self.dealt[1] + fl <= self.dealt[0]:
+                            self.dealt[1] += fl
+                            self.side_ids.update(x.id for x in ks_)
+                        else:
+                            self.dealt[0] += fl
                     q = 0
                     while q < len(run_kernels):
                         if q in astarts:
                             q = astarts[q][0]
                         elif q in hstarts:
+                            deal(run_kernels[q:hstarts[q][0]])
                             q = hstarts[q][0]
                         elif q in starts:
                             q = starts[q]
                         else:
-                            kq = run_kernels[q]          # (decided once, before the kernel's source exists; contractions stay)
-                            if kq.id in self.deferred and kq.id not in self.kernel_index and ct.match(kq) is None:
+                            kq = run_kernels[q]
+                            if ct.match(kq) is not None:
+                                deal([kq])
+                            elif kq.id in self.deferred and kq.id not in self.kernel_index:
                                 self.side_ids.add(kq.id)
                             q += 1
                 if in_loop and use_zgroups():
-                    self.plan_zgroups([kq for kq in run_kernels if kq.id in self.side_ids])
+                    self.plan_zgroups([kq for kq in run_kernels if kq.id in self.side_ids and ct.match(kq) is None])
                     # first-stream kernels: only neighbours that do not touch one another's results
                     q, singles = 0, []
                     while q < len(run_kernels):
@@ -2113,7 +2139,11 @@ class ProgramGen:
                         end, kind = hstarts[q]
                         ks = run_kernels[q:end]
                         gi = self.add_hgroup(ks, kind)
-                        calls.append(f"RT(launch_group_{gi}(rt));")
+                        if all(x.id in self.side_ids for x in ks):
+                            calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);")
+                            forked = True
+                        else:
+                            calls.append(f"RT(launch_group_{gi}(rt));")
                         if self.record_units:
                             self.hot_units.append((("g", gi), self.group_notes[gi], ks))
                         q = end

@@ -39,8 +39,13 @@ def test_every_fork_is_joined_inside_its_graph(monkeypatch):
     prog = load("c5_transformer")
     src, g = emit.generate(prog, seed=0)
     assert len(g.side_ids) >= 30 and all(i in g.deferred for i in g.side_ids)
-    # contractions keep the first stream (they want every SM and the first scratch region)
-    assert not any(g.kernel_notes[g.kernel_index[i]].startswith("gemm") for i in g.side_ids)
+    # deferred contractions (weight gradients with their updates) are dealt to the two streams by accumulated work
+    side_gemms = [i for i in g.side_ids if g.kernel_notes[g.kernel_index[i]].startswith("gemm")]
+    assert side_gemms and 0.8 < g.dealt[1] / g.dealt[0] < 1.25
+    for i in side_gemms:                                 # split-k partial sums of a second-stream product: second scratch region
+        body = g.kernel_src[g.kernel_index[i]]
+        if "_part" in body:
+            assert f"A + {g.plan.side_scratch_off}UL" in body and f"A + {g.plan.scratch_off}UL" not in body
     blocks = re.findall(r"anvil_rt_graph_begin\(rt, \d+\).*?anvil_rt_graph_end\(rt, \d+\)", src, flags=re.S)
     forked = [b for b in blocks if "anvil_rt_fork" in b]
     assert forked
@@ -72,8 +77,8 @@ def test_every_fork_is_joined_inside_its_graph(monkeypatch):
         assert max(t[1] for t in ticks) <= 256 and max(sp[1] for sp in spans) <= g.plan.side_scratch_bytes
         assert len(ids) <= g.ZGROUP_MAX
     # a side-by-side launch appears once, at its last member, between a fork and the join
-    z = re.findall(r"launch_group_(\d+)\(rt\)\); anvil_rt_back", src)
-    assert len(set(z)) == len([n for n in g.group_notes if n.startswith("zgroup")])
+    z = {int(x) for x in re.findall(r"launch_group_(\d+)\(rt\)\); anvil_rt_back", src)}
+    assert {i for i, n in enumerate(g.group_notes) if n.startswith("zgroup")} <= z      # (fused products may fork too)
     monkeypatch.setenv("ANVIL_B200_SIDE", "0")
     src0, g0 = emit.generate(load("c5_transformer"), seed=0)
     assert "anvil_rt_fork" not in src0 and not g0.side_ids
