@@ -1166,6 +1166,16 @@ def os_environ(name: str, default: str) -> str:
     return os.environ.get(name, default)
 
 
+def use_hoist() -> bool:
+    """Moving second-stream launches up to just after what they depend on (the weight gradients of a layer beside the
+    backward pass of the layers below) is built but off: measured on a B200 it does not shorten the step (14.37 against
+    14.27 ms). A resident kernel's CTAs hold their SMs until their statically assigned tiles are done, so a second
+    resident kernel gets SMs only as the first one's CTAs exit, wherever in the step it was launched. ANVIL_B200_HOIST=1
+    turns it on."""
+    import os
+    return os.environ.get("ANVIL_B200_HOIST", "0") == "1"
+
+
 def use_side_gemms() -> bool:
     import os
     return os.environ.get("ANVIL_B200_SIDE_GEMMS", "1") != "0"
@@ -2082,7 +2092,7 @@ class ProgramGen:
                         if not use_side_gemms() or any(x.id not in self.deferred or x.id in self.kernel_index for x in ks_):
                             return
                         fl = sum(an.kernel_flops(x) for x in ks_)
-                        if self.dealt[1] + fl <= self.dealt[0]:
+                        if os_environ("ANVIL_B200_SIDE_GEMMS", "1") == "all" or self.dealt[1] + fl <= self.dealt[0]:
                             self.dealt[1] += fl
                             self.side_ids.update(x.id for x in ks_)
                         else:
@@ -2126,12 +2136,19 @@ class ProgramGen:
                     if kj.id in skip and kj.uses_rand():      # fed from the host; its random stream is still consumed
                         calls.append("anvil_rt_set_stream(rt, anvil_rt_get_stream(rt) + 1u);")
                 forked = False
+                meta: dict = {}                      # index into calls -> (roots read, roots written, may move up: second stream, or tiny)
+
+                def launch(text, ks_, side=False):
+                    r_ = set().union(*[{b.id for b in x.reads()} for x in ks_])
+                    w_ = set().union(*[{b.id for b in x.writes()} for x in ks_])
+                    meta[len(calls)] = (r_, w_, side or all(x.out_numel() <= 1024 for x in ks_))
+                    calls.append(text)
                 q = 0
                 while q < len(run_kernels):
                     if q in astarts:
                         end, g = astarts[q]
                         gi = self.add_attention(g)
-                        calls.append(f"RT(launch_group_{gi}(rt));")
+                        launch(f"RT(launch_group_{gi}(rt));", g.kernels)
                         if self.record_units:
                             self.hot_units.append((("g", gi), self.group_notes[gi], g.kernels))
                         q = end
@@ -2140,17 +2157,17 @@ class ProgramGen:
                         ks = run_kernels[q:end]
                         gi = self.add_hgroup(ks, kind)
                         if all(x.id in self.side_ids for x in ks):
-                            calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);")
+                            launch(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);", ks, True)
                             forked = True
                         else:
-                            calls.append(f"RT(launch_group_{gi}(rt));")
+                            launch(f"RT(launch_group_{gi}(rt));", ks)
                         if self.record_units:
                             self.hot_units.append((("g", gi), self.group_notes[gi], ks))
                         q = end
                     elif q in starts:
                         ks = run_kernels[q:starts[q]]
                         gi = self.add_group(ks)
-                        calls.append(f"RT(launch_group_{gi}(rt));")
+                        launch(f"RT(launch_group_{gi}(rt));", ks)
                         if self.record_units:
                             self.hot_units.append((("g", gi), self.group_notes[gi], ks))
                         q = starts[q]
@@ -2166,22 +2183,42 @@ class ProgramGen:
                                 ks = [by_id[i_] for i_ in zg]
                                 gi = self.add_zgroup(ks)
                                 if zg[0] in self.side_ids:
-                                    calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);")
+                                    launch(f"RT(anvil_rt_fork(rt)); RT(launch_group_{gi}(rt)); anvil_rt_back(rt);", ks, True)
                                     forked = True
                                 else:
-                                    calls.append(f"RT(launch_group_{gi}(rt));")
+                                    launch(f"RT(launch_group_{gi}(rt));", ks)
                                 if self.record_units:
                                     self.hot_units.append((("g", gi), self.group_notes[gi], ks))
                         elif run_kernels[q].id in self.side_ids:
-                            calls.append(f"RT(anvil_rt_fork(rt)); RT(launch_{idx}(rt)); anvil_rt_back(rt);")
+                            launch(f"RT(anvil_rt_fork(rt)); RT(launch_{idx}(rt)); anvil_rt_back(rt);", [run_kernels[q]], True)
                             forked = True
                             if self.record_units:
                                 self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
                         else:
-                            calls.append(f"RT(launch_{idx}(rt));")
+                            launch(f"RT(launch_{idx}(rt));", [run_kernels[q]])
                             if self.record_units:
                                 self.hot_units.append((("k", idx), self.kernel_notes[idx], [run_kernels[q]]))
                         q += 1
+                if forked and use_hoist():
+                    # A second-stream launch only has to follow what it depends on: it moves up past every launch it
+                    # does not conflict with, so that it runs beside the first stream's chain instead of after it (the
+                    # weight gradients of a layer beside the backward pass of the layers below). So do the tiny kernels of
+                    # the first stream (the optimizer's step-dependent scalars, which every update waits for). A launch
+                    # stays where it is when it writes a tensor that shares arena bytes (those are planned in program order).
+                    order = [(calls[x], meta.get(x)) for x in range(len(calls))]
+                    for x in range(len(order)):
+                        m_ = order[x][1]
+                        if m_ is None or not m_[2] or (m_[1] & self.plan.shared):
+                            continue
+                        y = x
+                        while y > 0 and order[y - 1][1] is not None:
+                            r2, w2, _ = order[y - 1][1]
+                            if (m_[1] & (r2 | w2)) or (m_[0] & w2):
+                                break
+                            y -= 1
+                        if y < x:
+                            order.insert(y, order.pop(x))
+                    calls[:] = [t_ for t_, _ in order]
                 if forked:
                     calls.append("RT(anvil_rt_join(rt));")
                 if j == len(stmts) and tail is not None:
