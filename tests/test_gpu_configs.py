@@ -77,6 +77,19 @@ def test_free_running_trajectory(cfg):
     assert rel.max() <= bound, (int(rel.argmax()), float(rel.max()))
 
 
+def test_early_launch_of_second_stream_kernels(monkeypatch):
+    """ANVIL_B200_HOIST=1 (off by default: measured no faster) launches every second-stream kernel as early as what it
+    depends on allows, and all deferred contractions go to the second stream: the reduced transformer must still follow
+    the interpreter's trajectory."""
+    monkeypatch.setenv("ANVIL_B200_HOIST", "1")
+    monkeypatch.setenv("ANVIL_B200_SIDE_GEMMS", "all")
+    path = CONFIGS["c5_transformer_small"][0]
+    want = json.load(open(os.path.join(GOLDEN, "c5_transformer_small.losses.json")))["losses"][:40]
+    got = free_running(kir.load(path), len(want))
+    rel = np.abs(np.array(got) - np.array(want)) / np.abs(want)
+    assert rel.max() <= 1e-3, (int(rel.argmax()), float(rel.max()))
+
+
 def test_full_size_c5_first_steps():
     """The benchmark's own workload (6 layers, D 512, T 256, batch 64) against the reference interpreter run at
     full size: two steps is what the interpreter finishes in five hours (tests/golden/c5_transformer.losses.json,
