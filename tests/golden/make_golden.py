@@ -124,6 +124,8 @@ def do_traj(name, steps, consts=None, suffix=""):
     from anvil_lang_b200 import kir
     from anvil_lang_b200.backend.analysis import hot_loop
     path = os.path.join(ROOT, "anvil_lang_b200", "programs", f"{name}.anvil")
+    if not os.path.exists(path):                    # a test-only program
+        path = os.path.join(ROOT, "tests", "programs", f"{name}.anvil")
     c = compile_file(path, consts=consts)
     k = kir.from_anvil(c.program, name)
     hot = hot_loop(k)

@@ -4,7 +4,10 @@ the same IR kernels one after the other, on inputs copied from the oracle. Tenso
 are not compared (they are never written); everything it does write must match to 1e-4 of the tensor's magnitude
 (i32 exactly). The program is the transformer at T = 256 with two heads of 64 (the attention template's tile), batch 2,
 two layers; its IR and its first losses come from the reference front end and interpreter
-(`make_golden.py traj c5_transformer 4 '{"BATCH": 2, "LAYERS": 2, "D": 128, "HEADS": 2, "T": 256, "STEPS": 4}' _t256`)."""
+(`make_golden.py traj c5_transformer 4 '{"BATCH": 2, "LAYERS": 2, "D": 128, "HEADS": 2, "T": 256, "STEPS": 4}' _t256`).
+A second program has a band mask (`0.0 if j <= i + 64 else -1e9`, tests/programs/transformer_bandmask.anvil) instead of
+the causal one: the attention template then runs every query tile over all keys and takes the mask from the IR's own
+expression (`make_golden.py traj transformer_bandmask 3 '{... "STEPS": 3}' _t256`)."""
 import io
 import json
 import os
@@ -21,26 +24,28 @@ from util import GOLDEN, tensor_close
 
 pytestmark = pytest.mark.gpu
 
-PROGRAM = os.path.join(GOLDEN, "c5_transformer_t256.traj.kir.json.gz")
+PROGRAMS = ["c5_transformer_t256", "transformer_bandmask_t256"]
 
 
-def build(min_mflop="0"):
+def build(name, min_mflop="0"):
     os.environ["ANVIL_B200_TC_MIN_MFLOP"] = min_mflop          # the small products take the tensor-core templates too
     try:
-        prog = kir.load(PROGRAM)
+        prog = kir.load(os.path.join(GOLDEN, f"{name}.traj.kir.json.gz"))
         return prog, DeviceProgram(prog, seed=0, graphs=False)
     finally:
         os.environ.pop("ANVIL_B200_TC_MIN_MFLOP", None)
 
 
-def test_fused_launch_units_match_their_kernels_run_one_by_one():
-    prog, dp = build()
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_fused_launch_units_match_their_kernels_run_one_by_one(name):
+    prog, dp = build(name)
     hot = hot_loop(prog)
     o = Oracle(prog, out=io.StringIO(), seed=0, mode="fast")
     run_to_loop(o, prog, hot)
     nk = len(dp.gen.kernels)
     notes = [note for _, note, _ in dp.gen.hot_units]
     assert any(n.startswith("attention fwd") for n in notes) and any(n.startswith("attention bwd") for n in notes)
+    assert any(n.startswith("attention") and n.endswith("causal") for n in notes) == (name == "c5_transformer_t256")
     assert any("ncat" in n for n in notes) and any("kcat" in n for n in notes) and any(n.startswith("rowgroup") for n in notes)
     bad = []
     try:
@@ -70,9 +75,10 @@ def test_fused_launch_units_match_their_kernels_run_one_by_one():
     assert not bad, "\n".join(bad[:20])
 
 
-def test_first_losses_match_the_reference_interpreter():
-    want = json.load(open(os.path.join(GOLDEN, "c5_transformer_t256.losses.json")))["losses"]
-    prog, dp = build()
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_first_losses_match_the_reference_interpreter(name):
+    want = json.load(open(os.path.join(GOLDEN, f"{name}.losses.json")))["losses"]
+    prog, dp = build(name)
     try:
         dp.rtlib.anvil_rt_capture(dp.rt, 1)
         dp.prologue()
