@@ -2428,8 +2428,11 @@ class ProgramGen:
         # --profile: one row per launch unit, "name label strategy" like the native back end's "name label location"
         names = [f"{k.name:<6} {k.label[:34]:<34} {note}" for k, note in zip(self.kernels, self.kernel_notes)]
         by_idx = {idx: key for key, idx in self.groups.items()}
+        kinds = {"h": "fused products", "a": "fused attention", "z": "side by side"}
         for gi, note in enumerate(self.group_notes):
-            names.append(f"{'g%d' % gi:<6} {'fused rows':<34} {note}")
+            key = by_idx.get(gi, ())
+            what = kinds.get(key[0], "fused rows") if key and isinstance(key[0], str) else "fused rows"
+            names.append(f"{'g%d' % gi:<6} {what:<34} {note}")
         out.append(f"#define PROF_GROUP0 {len(self.kernels)}")
         out.append("static const char *const prof_names[] = {" + ", ".join(c_string(x) for x in names) + ("" if names else '""') + "};")
         out.append("")
