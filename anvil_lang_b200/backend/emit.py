@@ -20,6 +20,9 @@ for kernels, `CudaGen` :348-594 for host code), redesigned for B200:
     never touches device memory directly and synchronises only when the host needs a value
     (a printed scalar, an `if`/`while` condition, a run-time loop bound).
   * runs of kernel launches inside loops are recorded into CUDA graphs and replayed.
+  * several IR kernels may become one launch: runs of row kernels (`rowgroup`), products that share an operand or an
+    output (`hfuse`), attention runs (`attention`), and independent short kernels side by side (`plan_zgroups`);
+    kernels whose results nothing later in their launch run needs go to a second stream (`analysis.deferred_kernels`).
 
 Scalar expression semantics follow anvil/backend/cuda.py:110-199 (casts, wrap-around i32
 arithmetic, comparison results 0.0/1.0, nan-propagating max/min).
