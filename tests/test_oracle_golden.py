@@ -62,3 +62,25 @@ def test_config_losses_exist(cfg):
         pytest.skip("trajectory fixture not generated yet")
     d = json.load(open(path))
     assert len(d["losses"]) >= 20 and all(np.isfinite(d["losses"]))
+
+
+@pytest.mark.parametrize("name", ["c5_transformer_t256", "transformer_bandmask_t256"])
+def test_oracle_reproduces_the_interpreter_on_the_attention_fixtures(name):
+    """The T = 256 transformer fixtures (causal mask, and a band mask that takes the attention template's general
+    path on the device) carry losses printed by the reference interpreter itself: the restatement must reproduce
+    them bit for bit before it may check the device."""
+    import io
+    from anvil_lang_b200 import kir
+    from anvil_lang_b200.backend.analysis import hot_loop
+    from oracle.kir_interp import Oracle
+    from test_gpu_kernel_parity import run_to_loop
+    prog = kir.load(os.path.join(GOLDEN, f"{name}.traj.kir.json.gz"))
+    want = json.load(open(os.path.join(GOLDEN, f"{name}.losses.json")))["losses"]
+    hot = hot_loop(prog)
+    o = Oracle(prog, out=io.StringIO(), seed=0, mode="fast")
+    run_to_loop(o, prog, hot)
+    loss = [b for b in prog.roots() if b.name == "loss"][-1]
+    for step in range(2):
+        o.block(hot.body)
+        assert float(o.arr(loss)[0]) == want[step], (step, float(o.arr(loss)[0]), want[step])
+        o.arr(hot.counter)[0] += hot.step
